@@ -49,6 +49,8 @@ class RawConfig:
         if not isinstance(document, dict):
             raise ConfigError("config.json", "top level must be a JSON object")
         architectures = document.get("architectures") or []
+        if not architectures and isinstance(document.get("architecture"), str):
+            architectures = [document["architecture"]]           # documents that name their one design in the singular
         if not isinstance(architectures, list) or not all(isinstance(a, str) for a in architectures):
             raise ConfigError("config.json", "`architectures` must be a list of strings")
         eos = document.get("eos_token_id")

@@ -15,3 +15,16 @@ extern "C" int srb_paged_attention(const void* q, const void* k_pool, const void
                                   table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, split_size,
                                   max_splits, scale, error_word, dtype, stream);
 }
+
+// The same with the two optional terms: `sinks` (one float per query head, or null), values of `value_dim`
+// entries (0: as wide as the keys), and, with v_pool null, values that are the head of the key rows.
+extern "C" int srb_paged_attention_ex(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                      float* part_acc, float* part_ml, const int* positions,
+                                      const int* row_request, const int* block_table, int table_stride, int rows,
+                                      int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                      int split_size, int max_splits, float scale, int* error_word, int dtype,
+                                      const float* sinks, int value_dim, void* stream) {
+  return paged_attention_dispatch_ex(q, k_pool, v_pool, out, part_acc, part_ml, positions, row_request, block_table,
+                                     table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, split_size,
+                                     max_splits, scale, error_word, dtype, sinks, value_dim, stream);
+}

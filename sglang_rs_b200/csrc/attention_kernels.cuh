@@ -1,6 +1,6 @@
-// Attention over the paged cache, generic form: any head_dim up to 512, any number of
-// query heads per kv head up to 32, any page size, optional
-// window, 32-bit arithmetic throughout.  T is the storage type of q, the pages and the
+// Attention over the paged cache, generic form: any head_dim, any number of query heads per kv
+// head, any page size, optional window, optional sink per query head, values as wide as the keys or
+// narrower, 32-bit arithmetic throughout.  T is the storage type of q, the pages and the
 // output.  It is the whole attention of the 32-bit path and the fallback of the bfloat16
 // path for sizes its tensor-core kernels refuse.
 //
@@ -11,8 +11,16 @@
 // the causal length).  The running maximum and denominator follow the online form of
 // cuda_attention.rs:137-151.
 //
-// Work split: one block per (row, kv head, split); warp g of the block owns query head
-// kv_head * G + g.  Keys are visited in blocks of 32 aligned to absolute multiples of 32,
+// Two terms that other designs add, both off by default:
+//  * a sink: with `sinks` (one float per query head) the denominator also holds exp(sink_h), a term
+//    without key or value that is not scaled and counts once per row, however the keys are split;
+//  * values narrower than keys: the output and the value rows are `value_dim` wide.  With
+//    `shared_values` the value of a key is the first `value_dim` entries of its key row (a cache that
+//    keeps one latent row per token serves as key and as value), and v_pool is not read.
+//
+// Work split: one block per (row, kv head and chunk of its query heads, split); the block's warp w
+// owns query head kv_head * G + chunk * heads_per_block + w (at most 32 warps, so more than 32 query
+// heads per kv head go in several chunks).  Keys are visited in blocks of 32 aligned to absolute multiples of 32,
 // and a split covers `split_size` keys aligned to absolute multiples of split_size, so a
 // row's arithmetic depends on its own position only, never on how the step was cut or
 // what else is in the batch.  With split_size == 0 the block walks all keys and writes
@@ -35,6 +43,11 @@ struct AttnParams {
   int max_splits;
   float scale;
   int* error_word;
+  const float* sinks;        // [n_q] or null
+  int value_dim;             // width of a value row and of the output
+  int shared_values;         // 1: values are the first value_dim entries of the key rows
+  int head_chunks;           // blocks per (row, kv head, split) along the query heads
+  int heads_per_block;
 };
 
 __device__ __forceinline__ void row_key_range(const AttnParams& p, int pos, int split, int& lo, int& hi) {
@@ -62,24 +75,30 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
                                        float* __restrict__ part_acc, float* __restrict__ part_ml,
                                        AttnParams p) {
   extern __shared__ float smem[];
-  const int d = p.head_dim;
+  const int d = p.head_dim, vd = p.value_dim;
   const int groups = p.n_q / p.n_kv;
   float* k_tile = smem;                                  // [32][d + 1]
-  float* v_tile = k_tile + KEY_BLOCK * (d + 1);          // [32][d]
-  float* q_tile = v_tile + KEY_BLOCK * d;                // [groups][d]
+  float* v_tile = k_tile + KEY_BLOCK * (d + 1);          // [32][vd], or the key tile itself
+  float* q_tile = v_tile + (p.shared_values ? 0 : KEY_BLOCK * vd);   // [heads_per_block][d]
+  const int v_stride = p.shared_values ? d + 1 : vd;
+  if (p.shared_values) v_tile = k_tile;
   __shared__ long long key_offset[KEY_BLOCK];            // element offset of each key's row, -1 = masked
 
-  const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+  const int row = blockIdx.z, kv_head = blockIdx.y / p.head_chunks, chunk = blockIdx.y % p.head_chunks;
+  const int split = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[row];
   int lo, hi;
   row_key_range(p, pos, split, lo, hi);
   if (lo >= hi) return;
   const int request = p.row_request[row];
-  const int q_head = kv_head * groups + warp;
+  const int first_head = chunk * p.heads_per_block;      // within the kv head's group
+  const int here = min(p.heads_per_block, groups - first_head);
+  const bool live = warp < here;                         // a warp beyond the group's heads only helps to load
+  const int q_head = kv_head * groups + first_head + (live ? warp : 0);
 
-  for (int i = threadIdx.x; i < groups * d; i += blockDim.x)
-    q_tile[i] = srb_to_float(q[((size_t)row * p.n_q + (size_t)kv_head * groups) * d + i]);
+  for (int i = threadIdx.x; i < here * d; i += blockDim.x)
+    q_tile[i] = srb_to_float(q[((size_t)row * p.n_q + (size_t)kv_head * groups + first_head) * d + i]);
 
   float m = -INFINITY, l = 0.f;
   float acc[DIM_PER_LANE];
@@ -106,13 +125,19 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
       const int key = i / d, e = i - key * d;
       const long long offset = key_offset[key];
       k_tile[key * (d + 1) + e] = offset < 0 ? 0.f : srb_to_float(k_pool[offset + e]);
-      v_tile[key * d + e] = offset < 0 ? 0.f : srb_to_float(v_pool[offset + e]);
+    }
+    if (!p.shared_values) {
+      for (int i = threadIdx.x; i < KEY_BLOCK * vd; i += blockDim.x) {
+        const int key = i / vd, e = i - key * vd;
+        const long long offset = key_offset[key];          // in elements of a key row: rows are d or vd wide
+        v_tile[key * vd + e] = offset < 0 ? 0.f : srb_to_float(v_pool[offset / d * vd + e]);
+      }
     }
     __syncthreads();
 
     // one key per lane: the dot product runs over the head in index order
     float s = 0.f;
-    const float* qv = q_tile + warp * d;
+    const float* qv = q_tile + (live ? warp : 0) * d;
     const float* kv = k_tile + lane * (d + 1);
     for (int e = 0; e < d; ++e) s += qv[e] * kv[e];
     s = key_offset[lane] < 0 ? -INFINITY : s * p.scale;
@@ -129,24 +154,34 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 #pragma unroll
       for (int j = 0; j < DIM_PER_LANE; ++j) {
         const int e = lane + 32 * j;
-        if (e < d) acc[j] += pk * v_tile[key * d + e];
+        if (e < vd) acc[j] += pk * v_tile[key * v_stride + e];
       }
     }
   }
+  if (!live) return;
 
   if (p.split_size == 0) {
+    if (p.sinks) {
+      // the sink joins the denominator as one more term: exp(sink - M) with M the larger maximum
+      const float sink = p.sinks[q_head];
+      const float m_new = fmaxf(m, sink);
+      const float correction = expf(m - m_new);
+      l = l * correction + expf(sink - m_new);
+#pragma unroll
+      for (int j = 0; j < DIM_PER_LANE; ++j) acc[j] *= correction;
+    }
     const float inv = 1.0f / l;
 #pragma unroll
     for (int j = 0; j < DIM_PER_LANE; ++j) {
       const int e = lane + 32 * j;
-      if (e < d) out[((size_t)row * p.n_q + q_head) * d + e] = srb_from_float<T>(acc[j] * inv);
+      if (e < vd) out[((size_t)row * p.n_q + q_head) * vd + e] = srb_from_float<T>(acc[j] * inv);
     }
   } else {
     const size_t slot = ((size_t)row * p.n_q + q_head) * p.max_splits + split;
 #pragma unroll
     for (int j = 0; j < DIM_PER_LANE; ++j) {
       const int e = lane + 32 * j;
-      if (e < d) part_acc[slot * d + e] = acc[j];
+      if (e < vd) part_acc[slot * vd + e] = acc[j];
     }
     if (lane == 0) {
       part_ml[slot * 2] = m;
@@ -169,31 +204,31 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
   }
   const int count = min(wanted, p.max_splits);
   const size_t first = ((size_t)row * p.n_q + q_head) * p.max_splits;
-  float m = -INFINITY;
+  float m = p.sinks ? p.sinks[q_head] : -INFINITY;
   for (int s = 0; s < count; ++s) m = fmaxf(m, part_ml[(first + s) * 2]);
-  float l = 0.f;
+  float l = p.sinks ? expf(p.sinks[q_head] - m) : 0.f;   // the sink counts once, whatever the number of splits
   for (int s = 0; s < count; ++s) l += part_ml[(first + s) * 2 + 1] * expf(part_ml[(first + s) * 2] - m);
   const float inv = 1.0f / l;
-  for (int e = threadIdx.x; e < p.head_dim; e += blockDim.x) {
+  for (int e = threadIdx.x; e < p.value_dim; e += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < count; ++s)
-      acc += part_acc[(first + s) * p.head_dim + e] * expf(part_ml[(first + s) * 2] - m);
-    out[((size_t)row * p.n_q + q_head) * p.head_dim + e] = srb_from_float<T>(acc * inv);
+      acc += part_acc[(first + s) * p.value_dim + e] * expf(part_ml[(first + s) * 2] - m);
+    out[((size_t)row * p.n_q + q_head) * p.value_dim + e] = srb_from_float<T>(acc * inv);
   }
 }
 
 template <typename T, int DIM_PER_LANE>
 static int launch_attention(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_acc,
                             float* part_ml, const AttnParams& p, int rows, cudaStream_t s) {
-  const int groups = p.n_q / p.n_kv;
-  const size_t smem = ((size_t)KEY_BLOCK * (p.head_dim + 1) + (size_t)KEY_BLOCK * p.head_dim +
-                       (size_t)groups * p.head_dim) * sizeof(float);
+  const size_t smem = ((size_t)KEY_BLOCK * (p.head_dim + 1) + (p.shared_values ? 0 : (size_t)KEY_BLOCK * p.value_dim) +
+                       (size_t)p.heads_per_block * p.head_dim) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("paged_attention: %zu bytes of shared memory exceed 232448", smem);
   if (smem > 48 * 1024)
     SRB_CUDA_CALL(cudaFuncSetAttribute(paged_attention_kernel<T, DIM_PER_LANE>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(p.split_size == 0 ? 1 : p.max_splits, p.n_kv, rows);
-  paged_attention_kernel<T, DIM_PER_LANE><<<grid, groups * 32, smem, s>>>(
+  dim3 grid(p.split_size == 0 ? 1 : p.max_splits, p.n_kv * p.head_chunks, rows);
+  if (grid.y > 65535) SRB_FAIL("paged_attention: %d blocks along the heads exceed 65535", (int)grid.y);
+  paged_attention_kernel<T, DIM_PER_LANE><<<grid, p.heads_per_block * 32, smem, s>>>(
       (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, part_acc, part_ml, p);
   SRB_LAUNCH_CHECK("paged_attention");
   if (p.split_size != 0) {
@@ -205,18 +240,23 @@ static int launch_attention(const void* q, const void* k_pool, const void* v_poo
 }
 
 // Checks the sizes and launches; shared by every entry point.  Scratch (only when split_size > 0):
-// part_acc holds rows * n_q * max_splits * head_dim floats and part_ml rows * n_q * max_splits * 2.
-static int paged_attention_dispatch(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                   float* part_acc, float* part_ml, const int* positions,
-                                   const int* row_request, const int* block_table, int table_stride, int rows,
-                                   int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                   int split_size, int max_splits, float scale, int* error_word, int dtype,
-                                   void* stream) {
+// part_acc holds rows * n_q * max_splits * value_dim floats and part_ml rows * n_q * max_splits * 2.
+// `sinks` null: no sink.  `value_dim` 0: as wide as the keys.  `v_pool` null: the values are the first
+// value_dim entries of the key rows.
+static int paged_attention_dispatch_ex(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                       float* part_acc, float* part_ml, const int* positions,
+                                       const int* row_request, const int* block_table, int table_stride, int rows,
+                                       int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                       int split_size, int max_splits, float scale, int* error_word, int dtype,
+                                       const float* sinks, int value_dim, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0)
     SRB_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
-  if (n_q / n_kv > 32) SRB_FAIL("paged_attention: %d query heads per kv head exceed 32", n_q / n_kv);
-  if (head_dim <= 0 || head_dim > 512) SRB_FAIL("paged_attention: head_dim %d must be positive, at most 512", head_dim);
+  if (head_dim <= 0) SRB_FAIL("paged_attention: head_dim %d must be positive", head_dim);
+  if (value_dim == 0) value_dim = head_dim;
+  if (value_dim < 0 || value_dim > head_dim || value_dim > 1024)
+    SRB_FAIL("paged_attention: values of %d entries must be positive, at most as wide as the keys (%d) and at most 1024",
+             value_dim, head_dim);
   if (page_size <= 0 || num_pages <= 0 || table_stride <= 0)
     SRB_FAIL("paged_attention: page size, page count and table stride must be positive");
   if (window < 0 || split_size < 0) SRB_FAIL("paged_attention: window and split size must be non-negative");
@@ -231,8 +271,12 @@ static int paged_attention_dispatch(const void* q, const void* k_pool, const voi
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.split_size = split_size;
   p.max_splits = split_size == 0 ? 1 : max_splits; p.scale = scale; p.error_word = error_word;
+  p.sinks = sinks; p.value_dim = value_dim; p.shared_values = v_pool == nullptr;
+  const int groups = n_q / n_kv;
+  p.head_chunks = (groups + 31) / 32;
+  p.heads_per_block = (groups + p.head_chunks - 1) / p.head_chunks;
   cudaStream_t s = (cudaStream_t)stream;
-  const int per_lane = (head_dim + 31) / 32;
+  const int per_lane = (value_dim + 31) / 32;
 #define SRB_ATTN_CASE(T, N) \
   return launch_attention<T, N>(q, k_pool, v_pool, out, part_acc, part_ml, p, rows, s)
 #define SRB_ATTN_DISPATCH(T)                        \
@@ -240,8 +284,21 @@ static int paged_attention_dispatch(const void* q, const void* k_pool, const voi
   else if (per_lane <= 2) { SRB_ATTN_CASE(T, 2); }  \
   else if (per_lane <= 4) { SRB_ATTN_CASE(T, 4); }  \
   else if (per_lane <= 8) { SRB_ATTN_CASE(T, 8); }  \
-  else { SRB_ATTN_CASE(T, 16); }
+  else if (per_lane <= 16) { SRB_ATTN_CASE(T, 16); } \
+  else { SRB_ATTN_CASE(T, 32); }
   if (dtype == SRB_DTYPE_F32) { SRB_ATTN_DISPATCH(float) }
   if (dtype == SRB_DTYPE_BF16) { SRB_ATTN_DISPATCH(__nv_bfloat16) }
   SRB_FAIL("paged_attention: unknown dtype %d", dtype);
+}
+
+static int paged_attention_dispatch(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                   float* part_acc, float* part_ml, const int* positions,
+                                   const int* row_request, const int* block_table, int table_stride, int rows,
+                                   int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                   int split_size, int max_splits, float scale, int* error_word, int dtype,
+                                   void* stream) {
+  if (!v_pool) SRB_FAIL("paged_attention: the value pool is missing");
+  return paged_attention_dispatch_ex(q, k_pool, v_pool, out, part_acc, part_ml, positions, row_request, block_table,
+                                     table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, split_size,
+                                     max_splits, scale, error_word, dtype, nullptr, 0, stream);
 }

@@ -11,10 +11,10 @@
 SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
 
-// residual[row, :] = float(table[ids[row], :]); a bad id writes zeros and flags.
+// residual[row, :] = float(table[ids[row], :]) * scale; a bad id writes zeros and flags.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ residual, int width, int vocab, int* error_word) {
+                                 float* __restrict__ residual, int width, int vocab, int* error_word, float scale) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x;
@@ -30,14 +30,14 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
       float4 lo, hi;
       const float2 a = __bfloat1622float2(pair[0]), b = __bfloat1622float2(pair[1]);
       const float2 c = __bfloat1622float2(pair[2]), d = __bfloat1622float2(pair[3]);
-      lo = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a.x, a.y, b.x, b.y);
-      hi = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(c.x, c.y, d.x, d.y);
+      lo = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+      hi = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
       *reinterpret_cast<float4*>(dst + i) = lo;
       *reinterpret_cast<float4*>(dst + i + 4) = hi;
     }
     return;
   }
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = bad ? 0.f : srb_to_float(src[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = bad ? 0.f : srb_to_float(src[i]) * scale;
 }
 
 // x = residual[src] (+ delta[src]); optionally residual[src] = x; out[row] = T(x * rsqrt * w).
@@ -209,21 +209,27 @@ static int elementwise_grid(size_t total, int block) {
   return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
-extern "C" int srb_embedding(const int* ids, const void* table, float* residual, int rows, int width,
-                             int vocab, int* error_word, int dtype, void* stream) {
+// `scale` multiplies every value of the row in 32-bit (1 leaves the table's values as they are).
+extern "C" int srb_embedding_scaled(const int* ids, const void* table, float* residual, int rows, int width,
+                                    int vocab, int* error_word, int dtype, float scale, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (width <= 0 || vocab <= 0) SRB_FAIL("embedding: width %d and vocabulary %d must be positive", width, vocab);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(embedding_kernel<float>, dim3(rows), dim3(256), 0, s, ids, (const float*)table, residual,
-                             width, vocab, error_word));
+                             width, vocab, error_word, scale));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(embedding_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, ids,
-                             (const __nv_bfloat16*)table, residual, width, vocab, error_word));
+                             (const __nv_bfloat16*)table, residual, width, vocab, error_word, scale));
   else
     SRB_FAIL("embedding: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("embedding");
   return SRB_OK;
+}
+
+extern "C" int srb_embedding(const int* ids, const void* table, float* residual, int rows, int width,
+                             int vocab, int* error_word, int dtype, void* stream) {
+  return srb_embedding_scaled(ids, table, residual, rows, width, vocab, error_word, dtype, 1.0f, stream);
 }
 
 template <typename T>
@@ -276,6 +282,121 @@ extern "C" int srb_add_rmsnorm(float* residual, const void* delta, const float* 
     return launch_add_rmsnorm<__nv_bfloat16>(residual, delta, delta_parts, num_parts, (size_t)part_stride, weight,
                                              out, row_index, rows, width, eps, write_residual, s);
   SRB_FAIL("add_rmsnorm: unknown dtype %d", dtype);
+}
+
+// ---- a norm of the pending term, the residual sum, and the norm that follows, in one kernel ----------
+// x = residual[src] + inner(delta[src]); residual[src] = x if asked; out[row] = outer(x), rounded to T.
+// inner and outer are each one of
+//   SRB_NORM_NONE   v                                          (no weights)
+//   SRB_NORM_RMS    v / sqrt(mean(v^2) + eps) * w
+//   SRB_NORM_LAYER  (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w + b
+// with eps inside the root; every mean, the sum and the scaling are 32-bit.  The pending term arrives
+// in T (`delta`) or in float (`delta_f32`); with neither, x is the residual.  `extra` (optional, float,
+// [rows of residual, width]) is written, rounded, behind the row in `out` (columns width .. 2 width - 1):
+// the input of a product that reads the stream beside another one.  `out_pitch`: elements between rows of out.
+#define SRB_NORM_NONE 0
+#define SRB_NORM_RMS 1
+#define SRB_NORM_LAYER 2
+
+struct NormSpec {
+  int kind;
+  const float* weight;
+  const float* bias;
+  float eps;
+};
+
+// normalises `v` (width floats in shared memory) in place; every thread of the block calls it
+__device__ __forceinline__ void norm_in_place(float* v, int width, const NormSpec& n, float* scratch) {
+  if (n.kind == SRB_NORM_NONE) return;
+  float mean = 0.f;
+  if (n.kind == SRB_NORM_LAYER) {
+    float partial = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) partial += v[i];
+    mean = srb_block_sum(partial, scratch) / (float)width;
+  }
+  float partial = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float c = v[i] - mean;
+    partial += c * c;
+  }
+  const float inv = 1.0f / sqrtf(srb_block_sum(partial, scratch) / (float)width + n.eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float y = (v[i] - mean) * inv * n.weight[i];
+    if (n.kind == SRB_NORM_LAYER && n.bias) y += n.bias[i];
+    v[i] = y;
+  }
+  __syncthreads();
+}
+
+template <typename T>
+__global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                     const float* __restrict__ delta_f32, NormSpec inner, NormSpec outer,
+                                     T* __restrict__ out, size_t out_pitch, const float* __restrict__ extra,
+                                     const int* __restrict__ row_index, int width, int write_residual) {
+  extern __shared__ float staged[];          // width floats, then 33 floats of scratch
+  float* scratch = staged + width;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int row = blockIdx.x;
+  const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
+  const bool pending = delta || delta_f32;
+  if (pending) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      staged[i] = delta ? srb_to_float(delta[src + i]) : delta_f32[src + i];
+    __syncthreads();
+    norm_in_place(staged, width, inner, scratch);
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = residual[src + i];
+    if (pending) x += staged[i];
+    if (write_residual && pending) residual[src + i] = x;
+    staged[i] = x;
+  }
+  if (!out) return;
+  __syncthreads();
+  norm_in_place(staged, width, outer, scratch);
+  T* dst = out + (size_t)row * out_pitch;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = srb_from_float<T>(staged[i]);
+  if (extra)
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[width + i] = srb_from_float<T>(extra[src + i]);
+}
+
+extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+                                 const float* inner_weight, const float* inner_bias, float inner_eps, int outer_kind,
+                                 const float* outer_weight, const float* outer_bias, float outer_eps, void* out,
+                                 long long out_pitch, const float* extra, const int* row_index, int rows, int width,
+                                 int write_residual, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0) SRB_FAIL("norm_add_norm: width %d must be positive", width);
+  for (int kind : {inner_kind, outer_kind})
+    if (kind < SRB_NORM_NONE || kind > SRB_NORM_LAYER) SRB_FAIL("norm_add_norm: unknown kind of norm %d", kind);
+  if ((inner_kind != SRB_NORM_NONE && !inner_weight) || (out && outer_kind != SRB_NORM_NONE && !outer_weight))
+    SRB_FAIL("norm_add_norm: a norm without its weight");
+  if (!(inner_eps >= 0.f) || !(outer_eps >= 0.f)) SRB_FAIL("norm_add_norm: eps must be finite and non-negative");
+  if (out && out_pitch < (long long)width * (extra ? 2 : 1)) SRB_FAIL("norm_add_norm: rows of the output overlap");
+  const size_t smem = (size_t)(width + 33) * sizeof(float);
+  if (smem > 227 * 1024) SRB_FAIL("norm_add_norm: width %d needs %zu bytes of shared memory (limit 232448)", width, smem);
+  const NormSpec inner{inner_kind, inner_weight, inner_bias, inner_eps}, outer{outer_kind, outer_weight, outer_bias, outer_eps};
+  const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<float>, dim3(rows), dim3(block), smem, s, residual, (const float*)delta,
+                             delta_f32, inner, outer, (float*)out, (size_t)out_pitch, extra, row_index, width,
+                             write_residual));
+  } else if (dtype == SRB_DTYPE_BF16) {
+    if (smem > 48 * 1024)
+      SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(block), smem, s, residual,
+                             (const __nv_bfloat16*)delta, delta_f32, inner, outer, (__nv_bfloat16*)out, (size_t)out_pitch,
+                             extra, row_index, width, write_residual));
+  } else {
+    SRB_FAIL("norm_add_norm: unknown dtype %d", dtype);
+  }
+  SRB_LAUNCH_CHECK("norm_add_norm");
+  return SRB_OK;
 }
 
 extern "C" int srb_gated_mul(const void* gate_up, void* out, int rows, int inner, int activation, int dtype,

@@ -1,0 +1,313 @@
+// A feed-forward of routed experts: every row goes through `top` of `experts` small gated feed-forwards
+// and their results are summed with the router's weights.
+//
+//   srb_moe_route     logits = router . h in 32-bit, scores = softmax over all experts, the `top` largest are
+//                     chosen (ties: the lower index); weights are the chosen scores, or those divided by their
+//                     sum if `renormalize`
+//   srb_moe_plan      groups the (row, choice) entries by expert: a slot for each entry, the row of each slot, the
+//                     first slot of each expert, and the list of row tiles that the two products walk
+//   srb_moe_gated_up  act[slot, :] = activation(W_gate[e] h[row]) * (W_up[e] h[row])   for the slot's expert and row
+//   srb_moe_down      y[slot, :]   = W_down[e] act[slot]                              (32-bit result)
+//   srb_moe_combine   out[row, :]  = sum over the row's choices, in their order, of weight * y[slot]   (32-bit)
+//
+// Nothing here is decided on the host: counts, offsets and tiles stay on the device, the products are
+// launched for the largest number of tiles the step can need, and blocks without a tile leave at once.
+// Every output element is accumulated in 32-bit over the inner index in order by one thread, so a row's
+// result depends neither on the slot it got nor on the rows beside it.
+#include "common.cuh"
+#include "activations.cuh"
+#include <math.h>
+
+SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_PDL_SWITCH()
+
+#define MOE_TILE 64      // rows of a tile, and output columns of a block
+#define MOE_K 16
+#define MOE_MAX_EXPERTS 1024
+
+// One block per row.  Warps share the experts' dot products; warp 0 then picks the largest scores.
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ h, const T* __restrict__ router, int width, int experts, int top,
+                                 int renormalize, int* __restrict__ chosen, float* __restrict__ weights) {
+  __shared__ float score[MOE_MAX_EXPERTS];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const T* x = h + (size_t)row * width;
+  for (int e = warp; e < experts; e += warps) {
+    const T* w = router + (size_t)e * width;
+    float partial = 0.f;
+    for (int i = lane; i < width; i += 32) partial += srb_to_float(x[i]) * srb_to_float(w[i]);
+    partial = srb_warp_sum(partial);
+    if (lane == 0) score[e] = partial;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float top_logit = -INFINITY;
+  for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, score[e]);
+  top_logit = srb_warp_max(top_logit);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    const float p = expf(score[e] - top_logit);
+    score[e] = p;
+    sum += p;
+  }
+  sum = srb_warp_sum(sum);
+  __syncwarp();
+  float kept = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int best_index = experts;
+    for (int e = lane; e < experts; e += 32)
+      if (score[e] > best) { best = score[e]; best_index = e; }          // the first of equals within a lane
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+      if (other > best || (other == best && other_index < best_index)) { best = other; best_index = other_index; }
+    }
+    if (lane == 0) {
+      chosen[(size_t)row * top + k] = best_index;
+      weights[(size_t)row * top + k] = best / sum;
+      score[best_index] = -1.f;                                           // scores are positive: never chosen again
+    }
+    kept += best / sum;
+    __syncwarp();
+  }
+  if (renormalize && lane < top) weights[(size_t)row * top + lane] /= kept;
+}
+
+extern "C" int srb_moe_route(const void* h, const void* router, int rows, int width, int experts, int top, int renormalize,
+                             int* chosen, float* weights, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (experts <= 0 || experts > MOE_MAX_EXPERTS) SRB_FAIL("moe_route: %d experts are outside 1 .. %d", experts, MOE_MAX_EXPERTS);
+  if (top <= 0 || top > experts || top > 32) SRB_FAIL("moe_route: %d chosen experts are outside 1 .. min(%d, 32)", top, experts);
+  if (width <= 0) SRB_FAIL("moe_route: width %d must be positive", width);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int block = experts >= 8 ? 256 : 32 * experts;
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(moe_route_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)h, (const float*)router,
+                             width, experts, top, renormalize, chosen, weights));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(block), 0, s, (const __nv_bfloat16*)h,
+                             (const __nv_bfloat16*)router, width, experts, top, renormalize, chosen, weights));
+  else
+    SRB_FAIL("moe_route: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("moe_route");
+  return SRB_OK;
+}
+
+// One block.  plan: [0] number of tiles, then offsets[experts + 1], then per tile (expert, first slot).
+// slot_row[slot]: the row whose entry sits in the slot; entry_slot[row * top + k]: the slot of that entry.
+__global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int top, int experts, int max_tiles,
+                                int* __restrict__ plan, int* __restrict__ slot_row, int* __restrict__ entry_slot,
+                                int* error_word) {
+  __shared__ int count[MOE_MAX_EXPERTS];
+  __shared__ int first[MOE_MAX_EXPERTS + 1];
+  __shared__ int tile_first[MOE_MAX_EXPERTS + 1];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int slots = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = slots;
+      tile_first[e] = tiles;
+      slots += count[e];
+      tiles += (count[e] + MOE_TILE - 1) / MOE_TILE;
+    }
+    first[experts] = slots;
+    tile_first[experts] = tiles;
+    plan[0] = tiles <= max_tiles ? tiles : max_tiles;
+    if (tiles > max_tiles) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+  }
+  __syncthreads();
+  int* offsets = plan + 1;
+  int* tiles = plan + 1 + experts + 1;
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = first[e];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = tile_first[e + 1] - tile_first[e];
+    for (int t = 0; t < n; ++t) {
+      const int at = tile_first[e] + t;
+      if (at < max_tiles) {
+        tiles[2 * at] = e;
+        tiles[2 * at + 1] = first[e] + t * MOE_TILE;
+      }
+    }
+    count[e] = 0;                       // becomes the number of the expert's slots handed out so far
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = chosen[i];
+    if (e < 0 || e >= experts) { entry_slot[i] = -1; continue; }
+    const int slot = first[e] + atomicAdd(&count[e], 1);
+    slot_row[slot] = i / top;
+    entry_slot[i] = slot;
+  }
+}
+
+extern "C" int srb_moe_plan_ints(int rows, int top, int experts) {
+  const int max_tiles = (rows * top) / MOE_TILE + experts;
+  return 1 + experts + 1 + 2 * max_tiles;
+}
+
+extern "C" int srb_moe_max_tiles(int rows, int top, int experts) { return (rows * top) / MOE_TILE + experts; }
+
+extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, int* plan, int* slot_row, int* entry_slot,
+                            int* error_word, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0) SRB_FAIL("moe_plan: %d experts, %d chosen", experts, top);
+  SRB_CUDA_CALL(srb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, chosen, rows * top, top, experts,
+                           srb_moe_max_tiles(rows, top, experts), plan, slot_row, entry_slot, error_word));
+  SRB_LAUNCH_CHECK("moe_plan");
+  return SRB_OK;
+}
+
+// A tile of up to 64 slots of one expert times 64 output columns.  GATED: two weight matrices (gate, up), rows of
+// x gathered through slot_row, result act(gate) * up in T.  Otherwise one matrix, rows of x are the slots
+// themselves, result in float.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b,
+                   const int* __restrict__ plan, const int* __restrict__ slot_row, int experts, int n_in, int n_out,
+                   int activation, T* __restrict__ out_t, float* __restrict__ out_f) {
+  __shared__ float x_tile[MOE_K][MOE_TILE + 4];
+  __shared__ float a_tile[MOE_K][MOE_TILE + 4];
+  __shared__ float b_tile[GATED ? MOE_K : 1][MOE_TILE + 4];
+  __shared__ int tile_row[MOE_TILE];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* tiles = plan + 1 + experts + 1;
+  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
+  const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  const int t = threadIdx.x;
+  if (t < MOE_TILE) tile_row[t] = t < count ? (GATED ? slot_row[first + t] : first + t) : -1;
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int col0 = blockIdx.x * MOE_TILE;
+  const T* wa = w_a + (size_t)expert * n_out * n_in;
+  const T* wb = GATED ? w_b + (size_t)expert * n_out * n_in : nullptr;
+  float acc_a[4][4] = {}, acc_b[GATED ? 4 : 1][4] = {};
+  for (int k0 = 0; k0 < n_in; k0 += MOE_K) {
+    for (int i = threadIdx.x; i < MOE_TILE * MOE_K; i += 256) {
+      const int r = i / MOE_K, kk = i % MOE_K;
+      const int gk = k0 + kk;
+      const int source = tile_row[r];
+      x_tile[kk][r] = (source >= 0 && gk < n_in) ? srb_to_float(x[(size_t)source * n_in + gk]) : 0.f;
+      const bool inside = col0 + r < n_out && gk < n_in;
+      a_tile[kk][r] = inside ? srb_to_float(wa[(size_t)(col0 + r) * n_in + gk]) : 0.f;
+      if (GATED) b_tile[kk][r] = inside ? srb_to_float(wb[(size_t)(col0 + r) * n_in + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < MOE_K; ++kk) {
+      float xv[4], av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xv[i] = x_tile[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        av[j] = a_tile[kk][tx * 4 + j];
+        if (GATED) bv[j] = b_tile[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc_a[i][j] = fmaf(xv[i], av[j], acc_a[i][j]);
+          if (GATED) acc_b[i][j] = fmaf(xv[i], bv[j], acc_b[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= count) continue;
+    const size_t slot = (size_t)first + r;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx * 4 + j;
+      if (c >= n_out) continue;
+      if (GATED)
+        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], acc_b[i][j]));
+      else
+        out_f[slot * n_out + c] = acc_a[i][j];
+    }
+  }
+}
+
+template <typename T>
+static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
+                               const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
+                               void* out_t, float* out_f, cudaStream_t s) {
+  dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts));
+  if (grid.y > 65535) SRB_FAIL("moe product: %d tiles exceed one launch", (int)grid.y);
+  if (gated)
+    SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, true>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f));
+  else
+    SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, false>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f));
+  SRB_LAUNCH_CHECK("moe product");
+  return SRB_OK;
+}
+
+// h: [rows, width]; w_gate, w_up: [experts, inner, width]; act: [rows * top, inner]
+extern "C" int srb_moe_gated_up(const void* h, const void* w_gate, const void* w_up, const int* plan, const int* slot_row,
+                                int rows, int top, int experts, int width, int inner, int activation, void* act, int dtype,
+                                void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0 || inner <= 0) SRB_FAIL("moe_gated_up: sizes %d, %d must be positive", width, inner);
+  if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_gated_up: unknown activation %d", activation);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    return launch_moe_products<float>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, s);
+  if (dtype == SRB_DTYPE_BF16)
+    return launch_moe_products<__nv_bfloat16>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, s);
+  SRB_FAIL("moe_gated_up: unknown dtype %d", dtype);
+}
+
+// act: [rows * top, inner]; w_down: [experts, width, inner]; y: float [rows * top, width]
+extern "C" int srb_moe_down(const void* act, const void* w_down, const int* plan, int rows, int top, int experts, int width,
+                            int inner, float* y, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0 || inner <= 0) SRB_FAIL("moe_down: sizes %d, %d must be positive", width, inner);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    return launch_moe_products<float>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, s);
+  if (dtype == SRB_DTYPE_BF16)
+    return launch_moe_products<__nv_bfloat16>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, s);
+  SRB_FAIL("moe_down: unknown dtype %d", dtype);
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ entry_slot,
+                                   const float* __restrict__ weights, int top, int width, float* __restrict__ out) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int slot = entry_slot[(size_t)row * top + k];
+      if (slot >= 0) sum += weights[(size_t)row * top + k] * y[(size_t)slot * width + i];
+    }
+    out[(size_t)row * width + i] = sum;
+  }
+}
+
+extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
+                               float* out, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  SRB_CUDA_CALL(srb_launch(moe_combine_kernel, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, y,
+                           entry_slot, weights, top, width, out));
+  SRB_LAUNCH_CHECK("moe_combine");
+  return SRB_OK;
+}

@@ -4,7 +4,10 @@
 calls of one forward pass.  By default it is every layer once, in order, each with a cache
 of its own (reference: crates/sglang-srt/src/cpu_reference.rs:152-174).  A program may call
 a layer twice (two calls, two caches, one set of weights), and a call may read the cache
-of an earlier call instead of keeping one (it then writes nothing).
+of an earlier call instead of keeping one (it then writes nothing).  A call may also name a
+part of ``pass_entries`` that runs right before it: the head of a pass over a stretch of
+layers that the program walks several times (``parts/loop.py``); it is handed the stream,
+the embedding output and the number of the pass, and returns the new stream.
 """
 from __future__ import annotations
 
@@ -22,13 +25,18 @@ class LayerCall:
     layer: int
     #: index of an earlier call of the program whose cache this call reads; None = its own
     cache_from: Optional[int] = None
+    #: index into the model's ``pass_entries`` of the part that runs right before this call; None = nothing
+    entry: Optional[int] = None
+    #: the number of the pass that ``entry`` opens
+    pass_index: int = 0
 
 
 class DecoderModel(Part):
     def __init__(self, embedding, layers: Sequence, final_norm, head, *, vocab_size: int, max_positions: int,
                  program: Optional[Sequence[LayerCall]] = None, eos_token_ids: Sequence[int] = (),
-                 ignored_tensors: Sequence[str] = ()):
+                 ignored_tensors: Sequence[str] = (), pass_entries: Sequence = ()):
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
+        self.pass_entries = list(pass_entries)
         self.vocab_size, self.max_positions = int(vocab_size), int(max_positions)
         self.eos_token_ids = tuple(eos_token_ids)
         #: shell-style patterns of checkpoint tensors that may be present and that nothing reads
@@ -38,6 +46,8 @@ class DecoderModel(Part):
         for index, call in enumerate(self.program):
             if not 0 <= call.layer < len(self.layers):
                 raise ValueError(f"program entry {index} names layer {call.layer}, which does not exist")
+            if call.entry is not None and not 0 <= call.entry < len(self.pass_entries):
+                raise ValueError(f"program entry {index} names pass entry {call.entry}, which does not exist")
             if call.cache_from is not None:
                 if not 0 <= call.cache_from < index or self.program[call.cache_from].cache_from is not None:
                     raise ValueError(f"program entry {index} must read the cache of an earlier call that owns one")
@@ -51,7 +61,7 @@ class DecoderModel(Part):
         self.native = None
 
     def all_parts(self):
-        return [self.embedding, *self.layers, self.final_norm, self.head]
+        return [self.embedding, *self.pass_entries, *self.layers, self.final_norm, self.head]
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs: Dict[str, TensorSpec] = {}
@@ -77,10 +87,16 @@ class DecoderModel(Part):
             return self.native.run(ctx, caches, logit_rows)
         residual = self.embedding.forward(ctx, ctx.token_ids)
         delta = None
+        origin = None
+        if any(call.entry is not None for call in self.program):
+            # the embedding output as the pass entries read it; layers ahead of the first pass change the stream in place
+            origin = residual if self.program[0].entry is not None else residual.clone()
         for index, call in enumerate(self.program):
             cache = caches[index if call.cache_from is None else call.cache_from]
             if call.cache_from is not None and cache is not None:
                 cache = cache.read_only()
+            if call.entry is not None:
+                residual, delta = self.pass_entries[call.entry].forward(ctx, residual, delta, origin, call.pass_index), None
             residual, delta = self.layers[call.layer].forward(ctx, cache, residual, delta)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

@@ -142,15 +142,16 @@ def raise_on_error_value(value: int, word: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- rows
 
 @traced("embedding")
-def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, error_word: torch.Tensor) -> None:
-    """residual[r, :] = float(table[ids[r], :])"""
+def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, error_word: torch.Tensor,
+              scale: float = 1.0) -> None:
+    """residual[r, :] = float(table[ids[r], :]) * scale"""
     _need(ids, "ids", torch.int32); _need(table, "table"); _need(residual, "residual", torch.float32)
     rows, width = residual.shape
     if ids.numel() != rows or table.shape[1] != width:
         raise KernelError("embedding: shapes of ids, table and residual do not agree")
     lib = load_library("elementwise")
-    _check(lib, lib.srb_embedding(_ptr(ids), _ptr(table), _ptr(residual), rows, width, table.shape[0],
-                                  _ptr(error_word), dtype_code(table.dtype), _stream()))
+    _check(lib, lib.srb_embedding_scaled(_ptr(ids), _ptr(table), _ptr(residual), rows, width, table.shape[0],
+                                         _ptr(error_word), dtype_code(table.dtype), ctypes.c_float(scale), _stream()))
 
 
 @traced("embedding")
@@ -200,6 +201,70 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     _check(lib, lib.srb_add_rmsnorm(_ptr(residual), _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride),
                                     _ptr(weight), _ptr(out), _ptr(row_index), rows, width, ctypes.c_float(eps),
                                     int(write_residual), dtype_code(out.dtype), _stream()))
+
+
+#: kinds of norm that :func:`norm_add_norm` applies, by the numbers of csrc/elementwise.cu
+NORM_KINDS = {"none": 0, "rms": 1, "layer": 2}
+
+
+@traced("norm")
+def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, outer, out: Optional[torch.Tensor],
+                  row_index: Optional[torch.Tensor] = None, write_residual: bool = True,
+                  extra: Optional[torch.Tensor] = None) -> None:
+    """x = residual + inner(delta); residual = x if asked; out = outer(x), all sums and means in 32-bit.
+
+    ``inner`` and ``outer`` are ``(kind, weight, bias, eps)`` with kind one of ``NORM_KINDS`` (``none``: the
+    identity; ``rms``: v / sqrt(mean(v^2) + eps) * w; ``layer``: (v - mean) / sqrt(var + eps) * w + b) or None
+    for the identity.  ``delta`` is [rows, width] of ``out``'s dtype or float32, or None (x is the residual).
+    ``out`` may be None (only the sum is wanted) and may have rows longer than ``width``; with ``extra``
+    (float32, shaped like the residual) its rows are written, rounded, into columns width .. 2 width - 1 of out."""
+    _need(residual, "residual", torch.float32)
+    width = residual.shape[1]
+    def spec(norm):
+        if norm is None:
+            return 0, None, None, 0.0
+        kind, weight, bias, eps = norm
+        for name, tensor in (("weight", weight), ("bias", bias)):
+            if tensor is not None:
+                _need(tensor, name, torch.float32)
+                if tensor.numel() != width:
+                    raise KernelError(f"norm_add_norm: a norm's {name} must have {width} entries")
+        return NORM_KINDS[kind], weight, bias, float(eps)
+    inner_kind, inner_w, inner_b, inner_eps = spec(inner)
+    outer_kind, outer_w, outer_b, outer_eps = spec(outer)
+    whole = as_float = None
+    if delta is not None:
+        _need(delta, "delta")
+        if delta.shape != residual.shape:
+            raise KernelError("norm_add_norm: delta and residual differ in shape")
+        if delta.dtype == torch.float32 and (out is None or out.dtype != torch.float32):
+            as_float = delta
+        else:
+            whole = delta
+    rows = residual.shape[0] if row_index is None else row_index.numel()
+    pitch = 0
+    dtype = residual.dtype if out is None else out.dtype
+    if out is not None:
+        if out.dim() != 2 or out.stride(1) != 1 or out.shape[0] != rows or not out.is_cuda:
+            raise KernelError("norm_add_norm: out must be a CUDA matrix with dense rows, one per row")
+        pitch = out.stride(0)
+        if out.shape[1] < width * (2 if extra is not None else 1):
+            raise KernelError("norm_add_norm: rows of out are too short")
+    elif whole is not None:
+        dtype = whole.dtype
+    if whole is not None and whole.dtype != dtype:
+        raise KernelError("norm_add_norm: delta must be float32 or of out's dtype")
+    if extra is not None:
+        _need(extra, "extra", torch.float32)
+        if extra.shape != residual.shape:
+            raise KernelError("norm_add_norm: extra and residual differ in shape")
+    if row_index is not None:
+        _need(row_index, "row_index", torch.int32)
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_norm_add_norm(
+        _ptr(residual), _ptr(whole), _ptr(as_float), inner_kind, _ptr(inner_w), _ptr(inner_b), ctypes.c_float(inner_eps),
+        outer_kind, _ptr(outer_w), _ptr(outer_b), ctypes.c_float(outer_eps), _ptr(out), ctypes.c_longlong(pitch),
+        _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _stream()))
 
 
 #: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh
@@ -319,31 +384,44 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
                     scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
-                    error_word: torch.Tensor) -> None:
+                    error_word: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
     """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
+
+    ``sinks`` (float32, one per query head): the softmax's denominator also holds exp(sink_h), a term without
+    key or value.  ``v_pool`` may hold rows narrower than the keys (``out`` is as wide as they are), and may be
+    None: the value of a key is then the first ``out.shape[2]`` entries of its key row.
 
     q, out: [rows, n_q, head_dim]; pools [pages, n_kv, page_size, head_dim]; block_table
     [requests, stride].  ``split_size`` 0 walks all keys in one block per (row, kv head);
     otherwise partials go through the scratch tensors and are merged in split order.
     This is the generic kernel (any head_dim that is a multiple of 16, float32 or bfloat16)."""
-    _need(q, "q"); _need(out, "out", q.dtype); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
+    _need(q, "q"); _need(out, "out", q.dtype); _need(k_pool, "k_pool", q.dtype)
     _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
     _need(block_table, "block_table", torch.int32)
     rows, n_q, head_dim = q.shape
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
-    if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape:
+    value_dim = out.shape[2]
+    if pool_dim != head_dim or out.shape[:2] != q.shape[:2] or value_dim > head_dim:
         raise KernelError("paged_attention: shapes of q, out and the pools do not agree")
+    if v_pool is not None:
+        _need(v_pool, "v_pool", q.dtype)
+        if v_pool.shape != (*k_pool.shape[:3], value_dim):
+            raise KernelError("paged_attention: the value pool must be [pages, n_kv, page_size, width of out]")
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_q:
+            raise KernelError("paged_attention: one sink per query head is needed")
     if split_size:
-        need_acc, need_ml = attention_scratch_sizes(rows, n_q, head_dim, max_splits)
+        need_acc, need_ml = attention_scratch_sizes(rows, n_q, value_dim, max_splits)
         if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
     lib = load_library("attention")
-    _check(lib, lib.srb_paged_attention(
+    _check(lib, lib.srb_paged_attention_ex(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
         _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
         num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
-        dtype_code(q.dtype), _stream()), launches=2 if split_size else 1)
+        dtype_code(q.dtype), _ptr(sinks), value_dim, _stream()), launches=2 if split_size else 1)
 
 
 
@@ -469,6 +547,139 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], rows, _ptr(block_table),
         block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), ctypes.c_float(scale),
         _ptr(error_word), _stream()))
+
+
+# --------------------------------------------------------------------------- latents and per-head products
+
+@traced("rope_kv")
+def latent_prepare(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
+                   kv_weight: torch.Tensor, eps: float, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                   rotary_dim: int, q_latent: Optional[torch.Tensor], pool: Optional[torch.Tensor],
+                   slots: Optional[torch.Tensor], error_word: torch.Tensor) -> None:
+    """Rows of ``proj`` hold [query latent (q_rank) | key/value latent (kv_rank) | shared key part (rot_dim) | ...].
+    ``q_latent[r]`` = RMS norm of the first; the row's slot of ``pool`` ([pages, 1, page_size, kv_rank + rot_dim])
+    receives the RMS norm of the second and the rotated third.  ``slots`` None: nothing is stored."""
+    _need(positions, "positions", torch.int32); _need(kv_weight, "kv_weight", torch.float32)
+    if proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("latent_prepare: proj must be a CUDA matrix with dense rows")
+    rows = proj.shape[0]
+    if proj.shape[1] < q_rank + kv_rank + rot_dim:
+        raise KernelError("latent_prepare: rows of proj are too short")
+    if q_rank:
+        _need(q_latent, "q_latent", proj.dtype); _need(q_weight, "q_weight", torch.float32)
+        if q_latent.shape != (rows, q_rank) or q_weight.numel() != q_rank:
+            raise KernelError("latent_prepare: the query latent must be [rows, q_rank]")
+    pool_rows = 0
+    if slots is not None:
+        _need(slots, "slots", torch.int32); _need(pool, "pool", proj.dtype)
+        if pool.shape[-1] != kv_rank + rot_dim or pool.shape[1] != 1:
+            raise KernelError("latent_prepare: the pool must be [pages, 1, page_size, kv_rank + rot_dim]")
+        pool_rows = pool.shape[0] * pool.shape[2]
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("latent_prepare: inv_freq must have rotary_dim / 2 entries")
+    lib = load_library("latent")
+    _check(lib, lib.srb_latent_prepare(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), rows, q_rank, kv_rank, rot_dim, _ptr(q_weight), _ptr(kv_weight),
+        ctypes.c_float(eps), _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(q_latent), _ptr(pool), _ptr(slots),
+        ctypes.c_longlong(pool_rows), _ptr(error_word), dtype_code(proj.dtype), _stream()))
+
+
+@traced("rope_kv")
+def rope_slice(x: torch.Tensor, in_offset: int, out: torch.Tensor, out_offset: int, width: int, rotary_dim: int,
+               positions: torch.Tensor, inv_freq: Optional[torch.Tensor]) -> None:
+    """out[r, h, out_offset + i] = rotated(x[r, h, in_offset + i]), i < width, pairs (i, i + rotary_dim / 2);
+    entries from ``rotary_dim`` on are copied.  x, out: [rows, heads, *] with dense last axis."""
+    _need(x, "x"); _need(out, "out", x.dtype); _need(positions, "positions", torch.int32)
+    if x.dim() != 3 or out.dim() != 3 or x.shape[:2] != out.shape[:2]:
+        raise KernelError("rope_slice: x and out must be [rows, heads, *]")
+    if in_offset + width > x.shape[2] or out_offset + width > out.shape[2]:
+        raise KernelError("rope_slice: the slice does not fit")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rope_slice: inv_freq must have rotary_dim / 2 entries")
+    lib = load_library("latent")
+    _check(lib, lib.srb_rope_slice(
+        _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), in_offset, _ptr(out),
+        ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)), out_offset, x.shape[0], x.shape[1], width,
+        rotary_dim, _ptr(positions), _ptr(inv_freq), dtype_code(x.dtype), _stream()))
+
+
+@traced("gemm")
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """out[r, h, :n_out] = weight[h] @ x[r, h, :n_in] with ``weight`` [heads, n_out, n_in]; x and out are views
+    [rows, heads, >= n] with a dense last axis.  ``gate`` ([rows, >= heads] view of logits): head h's result is
+    multiplied by sigmoid(gate[r, h])."""
+    heads, n_out, n_in = weight.shape
+    _need(weight, "weight", x.dtype)
+    if (x.dim() != 3 or out.dim() != 3 or x.shape[1] != heads or out.shape[1] != heads or x.shape[0] != out.shape[0]
+            or x.shape[2] < n_in or out.shape[2] < n_out or x.stride(2) != 1 or out.stride(2) != 1 or out.dtype != x.dtype):
+        raise KernelError("head_linear: x, weight and out do not fit")
+    gate_row = 0
+    if gate is not None:
+        if gate.dim() != 2 or gate.shape[0] != x.shape[0] or gate.shape[1] < heads or gate.stride(1) != 1 or gate.dtype != x.dtype:
+            raise KernelError("head_linear: gate must be [rows, heads] of x's dtype with a dense last axis")
+        gate_row = gate.stride(0)
+    lib = load_library("latent")
+    _check(lib, lib.srb_head_linear(
+        _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(weight), _ptr(out),
+        ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)), x.shape[0], heads, n_in, n_out, _ptr(gate),
+        ctypes.c_longlong(gate_row), dtype_code(x.dtype), _stream()))
+
+
+# --------------------------------------------------------------------------- routed experts
+
+@traced("gemm")
+def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                   top: int, activation: str, renormalize: bool, error_word: torch.Tensor) -> torch.Tensor:
+    """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].
+
+    ``router`` [experts, width]; ``w_gate``, ``w_up`` [experts, inner, width]; ``w_down`` [experts, width, inner],
+    all of h's dtype.  Scores are a softmax over all experts, in 32-bit; with ``renormalize`` the chosen ones are
+    divided by their sum.  Five launches, nothing decided on the host."""
+    _need(h, "h"); _need(router, "router", h.dtype); _need(w_gate, "w_gate", h.dtype); _need(w_up, "w_up", h.dtype)
+    _need(w_down, "w_down", h.dtype)
+    rows, width = h.shape
+    experts, inner = w_gate.shape[0], w_gate.shape[1]
+    if (router.shape != (experts, width) or w_gate.shape != (experts, inner, width) or w_up.shape != w_gate.shape
+            or w_down.shape != (experts, width, inner)):
+        raise KernelError("routed_experts: shapes of the router and the experts do not agree")
+    lib = load_library("moe")
+    device = h.device
+    entries = rows * top
+    chosen = torch.empty(entries, dtype=torch.int32, device=device)
+    weights = torch.empty(entries, dtype=torch.float32, device=device)
+    plan = torch.empty(lib.srb_moe_plan_ints(rows, top, experts), dtype=torch.int32, device=device)
+    slot_row = torch.empty(entries, dtype=torch.int32, device=device)
+    entry_slot = torch.empty(entries, dtype=torch.int32, device=device)
+    act = torch.empty((entries, inner), dtype=h.dtype, device=device)
+    y = torch.empty((entries, width), dtype=torch.float32, device=device)
+    out = torch.empty((rows, width), dtype=torch.float32, device=device)
+    code, stream = dtype_code(h.dtype), _stream()
+    _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, experts, top, int(renormalize), _ptr(chosen),
+                                  _ptr(weights), code, stream))
+    _check(lib, lib.srb_moe_plan(_ptr(chosen), rows, top, experts, _ptr(plan), _ptr(slot_row), _ptr(entry_slot),
+                                 _ptr(error_word), stream))
+    _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slot_row), rows, top, experts,
+                                     width, inner, activation_code(activation), _ptr(act), code, stream))
+    _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
+                                 stream))
+    _check(lib, lib.srb_moe_combine(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), stream))
+    return out
+
+
+def route(h: torch.Tensor, router: torch.Tensor, top: int, renormalize: bool = False):
+    """The router alone: (chosen experts int32 [rows, top], their weights float32 [rows, top])."""
+    _need(h, "h"); _need(router, "router", h.dtype)
+    rows, width = h.shape
+    chosen = torch.empty((rows, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((rows, top), dtype=torch.float32, device=h.device)
+    lib = load_library("moe")
+    _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, router.shape[0], top, int(renormalize), _ptr(chosen),
+                                  _ptr(weights), dtype_code(h.dtype), _stream()))
+    return chosen, weights
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -1,14 +1,18 @@
 from .attention import AttentionNames, GroupedQueryAttention
-from .base import (CacheNeed, FeedForward, Mixer, Norm, PagedKV, Part, PositionEncoding, RequestState, TensorSpec,
-                   matrix_to, scale_to)
-from .block import PreNormBlock
+from .base import (CacheNeed, FeedForward, Mixer, Norm, NormedDelta, PagedKV, Part, PositionEncoding, RequestState,
+                   TensorSpec, matrix_to, scale_to)
+from .block import PreNormBlock, SandwichBlock
+from .latent_attention import LatentAttention, LatentAttentionNames
+from .loop import PassEntry
+from .moe import RoutedExperts
 from .embedding import OutputHead, TokenEmbedding
 from .mlp import GatedMlp, GatedMlpNames
-from .norm import RmsNorm
+from .norm import LayerNorm, RmsNorm
 from .rope import NoPositionEncoding, RotaryEncoding
 
 __all__ = [
     "AttentionNames", "GroupedQueryAttention", "CacheNeed", "FeedForward", "Mixer", "Norm", "PagedKV", "Part",
     "PositionEncoding", "RequestState", "TensorSpec", "matrix_to", "scale_to", "PreNormBlock", "OutputHead",
-    "TokenEmbedding", "GatedMlp", "GatedMlpNames", "RmsNorm", "NoPositionEncoding", "RotaryEncoding",
+    "TokenEmbedding", "GatedMlp", "GatedMlpNames", "RmsNorm", "NoPositionEncoding", "RotaryEncoding", "NormedDelta",
+    "SandwichBlock", "LatentAttention", "LatentAttentionNames", "PassEntry", "RoutedExperts", "LayerNorm",
 ]

@@ -37,10 +37,12 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """A mixer that keeps keys and values per token.  ``window`` None keeps all of them;
-    a number keeps only what the last ``window`` positions can still see."""
+    a number keeps only what the last ``window`` positions can still see.  ``values`` False keeps one
+    row per token and kv head only (a latent that serves as key and as value): no value pool is made."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -66,7 +68,23 @@ class Part:
         pass
 
 
+@dataclass
+class NormedDelta:
+    """A pending term of the residual sum that is normalised before it is added: the hidden state is
+    ``residual + norm(values)``.  Blocks whose sublayers end in a norm hand it on like this, so that the
+    norm, the sum and the next norm run in one kernel."""
+    values: torch.Tensor
+    norm: "Norm"
+
+
 class Norm(Part):
+    #: the kernels' name of the norm ("rms", "layer")
+    kind = "rms"
+
+    def spec(self):
+        """(kind, weight, bias, eps) as :func:`ops.norm_add_norm` takes it."""
+        raise NotImplementedError
+
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError

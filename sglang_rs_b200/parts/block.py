@@ -11,7 +11,7 @@ from typing import Dict, Mapping, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, Part, TensorSpec
+from .base import FeedForward, Mixer, Norm, NormedDelta, Part, TensorSpec
 
 
 class PreNormBlock(Part):
@@ -58,3 +58,51 @@ class PreNormBlock(Part):
         normed = self.post_norm.add_norm(residual, delta, ctx.dtype)
         delta = self.feed_forward.forward(ctx, normed)
         return residual, delta
+
+
+class SandwichBlock(Part):
+    """A norm ahead of and behind each sublayer: h' = h + norm_1b(mixer(norm_1(h))),
+    h'' = h' + norm_2b(feed_forward(norm_2(h'))); without a feed-forward the block ends after the mixer.
+
+    The hidden state travels as (residual, pending) with the pending term a :class:`NormedDelta`: the norm
+    behind a sublayer, the residual sum and the norm ahead of the next sublayer are one kernel
+    (``Norm.add_norm``), also across the border between two blocks."""
+
+    def __init__(self, norm_1: Norm, mixer: Mixer, norm_1b: Norm, norm_2: Optional[Norm] = None,
+                 feed_forward: Optional[FeedForward] = None, norm_2b: Optional[Norm] = None):
+        if (feed_forward is None) != (norm_2 is None) or (feed_forward is None) != (norm_2b is None):
+            raise ValueError("a feed-forward comes with the norms ahead of and behind it, or not at all")
+        self.norm_1, self.mixer, self.norm_1b = norm_1, mixer, norm_1b
+        self.norm_2, self.feed_forward, self.norm_2b = norm_2, feed_forward, norm_2b
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts())
+
+    def parts(self):
+        return tuple(part for part in (self.norm_1, self.mixer, self.norm_1b, self.norm_2, self.feed_forward,
+                                       self.norm_2b) if part is not None)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def split_scratch(self):
+        return self.mixer.split_scratch()
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs: Dict[str, TensorSpec] = {}
+        for part in self.parts():
+            specs.update(part.tensor_specs())
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        for part in self.parts():
+            part.load(tensors, device, dtype)
+
+    def forward(self, ctx, cache, residual: torch.Tensor, delta):
+        normed = self.norm_1.add_norm(residual, delta, ctx.dtype)
+        delta = NormedDelta(self.mixer.forward(ctx, cache, normed), self.norm_1b)
+        if self.feed_forward is None:
+            return residual, delta
+        normed = self.norm_2.add_norm(residual, delta, ctx.dtype)
+        return residual, NormedDelta(self.feed_forward.forward(ctx, normed), self.norm_2b)

@@ -1,6 +1,6 @@
 """Token embedding and output head.
 
-h0 = embed[token] without scaling; logits = norm(h) . W_out^T with W_out the head's own
+h0 = embed[token] * scale (scale 1 unless the architecture says otherwise; the product is 32-bit); logits = norm(h) . W_out^T with W_out the head's own
 matrix or, if tied, the embedding table (reference:
 crates/sglang-srt/src/cpu_reference.rs:741-752, :176-185).  Logits are 32-bit in every mode.
 """
@@ -17,8 +17,8 @@ from .base import Part, TensorSpec, matrix_to
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, width: int, weight_name: str):
-        self.vocab, self.width, self.weight_name = int(vocab), int(width), weight_name
+    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0):
+        self.vocab, self.width, self.weight_name, self.scale = int(vocab), int(width), weight_name, float(scale)
         self.table: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -28,12 +28,12 @@ class TokenEmbedding(Part):
         self.table = matrix_to(tensors[self.weight_name], device, dtype)
 
     def native_record(self):
-        """The step executor reads the table itself; the record says only that there is one."""
-        return None if self.table is None else True
+        """The step executor reads the table itself; the record says only that there is one (it knows no scale)."""
+        return None if self.table is None or self.scale != 1.0 else True
 
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
         residual = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
-        ops.embedding(token_ids, self.table, residual, ctx.error_word)
+        ops.embedding(token_ids, self.table, residual, ctx.error_word, self.scale)
         return residual
 
 

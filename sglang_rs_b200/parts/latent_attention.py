@@ -1,0 +1,136 @@
+"""Attention through latents, with a sink per head and an output gate.
+
+For the mixer's input h (one row per token):
+
+* queries: c_q = RMSnorm(W_dq h) * w_dq, q = W_uq c_q, head by head [dim plain | rot_dim rotated];
+* keys and values: W_dkv h = [kv_rank | rot_dim]; c = RMSnorm(first part) * w_dkv is the latent, the
+  second part (not normed) is one rotated key part that all heads share; per head k_plain = W_uk c and
+  v = W_uv c;
+* score(i, j) = (q_plain_i . k_plain_j + q_rot_i . k_rot_j) * scale for j <= i; softmax whose denominator
+  also holds exp(sink_h); head h's result is multiplied by sigmoid(W_g h)_h; W_o on the joined heads.
+
+Only c and the rotated key part are kept per token: one pool row [kv_rank + rot_dim], one "kv head".
+The up-projections never touch the cache: since q_plain . (W_uk c) = (W_uk^T q_plain) . c, each query
+head is carried into the latent space (``head_linear`` with W_uk^T per head), attention then runs over
+the cached rows themselves with ``heads`` query heads on one shared key row whose first kv_rank
+entries are also the value, and W_uv is applied per head to the attention's result (with the gate in
+the same kernel).  Scores, softmax, norms and angles are 32-bit in both dtypes.
+
+W_dq, W_dkv and W_g read the same input and are one product (rows stacked at load).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import ops
+from .base import Mixer, PagedKV, TensorSpec, matrix_to, scale_to
+from .rope import RotaryEncoding
+
+
+@dataclass(frozen=True)
+class LatentAttentionNames:
+    q_down: str
+    q_norm: str
+    q_up: str
+    kv_down: str
+    kv_norm: str
+    k_up: str
+    v_up: str
+    o: str
+    sink: Optional[str] = None
+    gate: Optional[str] = None
+
+
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, hidden: int, num_heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
+                 scale: float, eps: float, rotary: Optional[RotaryEncoding], names: LatentAttentionNames):
+        """``rotary``: the rotation of the rot_dim part (its ``rotary_dim`` leading entries are rotated, the rest
+        pass unchanged); None leaves it alone.  ``names.sink`` / ``names.gate`` None: no sink / no gate."""
+        for name, value in (("heads", num_heads), ("dim", dim), ("vdim", value_dim), ("q_rank", q_rank), ("kv_rank", kv_rank)):
+            if value <= 0:
+                raise ValueError(f"latent attention: {name} must be positive, found {value}")
+        if rot_dim < 0 or (rotary is not None and rotary.rotary_dim > rot_dim):
+            raise ValueError(f"latent attention: the rotation covers more than the {rot_dim} rotated entries")
+        if rotary is not None and rotary.interleaved:
+            raise ValueError("latent attention: only the half-split pairing of rotated entries is built")
+        if kv_rank > 1024:
+            raise ValueError(f"latent attention: a latent of {kv_rank} entries exceeds the 1024 the attention kernel takes")
+        self.hidden, self.heads, self.dim, self.rot_dim, self.vdim = int(hidden), int(num_heads), int(dim), int(rot_dim), int(value_dim)
+        self.q_rank, self.kv_rank, self.scale, self.eps = int(q_rank), int(kv_rank), float(scale), float(eps)
+        self.rotary, self.names = rotary, names
+        self.w_in = self.w_uq = self.w_qk = self.w_uv = self.w_o = self.q_norm = self.kv_norm = self.sink = None
+
+    @property
+    def row_width(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+    def cache_need(self) -> PagedKV:
+        return PagedKV(1, self.row_width, None, values=False)
+
+    def split_scratch(self):
+        return (self.heads * self.kv_rank, self.heads * 2)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        n, h = self.names, self.heads
+        specs = {
+            n.q_down: TensorSpec((self.q_rank, self.hidden)), n.q_norm: TensorSpec((self.q_rank,), "scale"),
+            n.q_up: TensorSpec((h * (self.dim + self.rot_dim), self.q_rank)),
+            n.kv_down: TensorSpec((self.kv_rank + self.rot_dim, self.hidden)), n.kv_norm: TensorSpec((self.kv_rank,), "scale"),
+            n.k_up: TensorSpec((h * self.dim, self.kv_rank)), n.v_up: TensorSpec((h * self.vdim, self.kv_rank)),
+            n.o: TensorSpec((self.hidden, h * self.vdim)),
+        }
+        if n.sink:
+            specs[n.sink] = TensorSpec((h,))
+        if n.gate:
+            specs[n.gate] = TensorSpec((h, self.hidden))
+        if self.rotary is not None:
+            specs.update(self.rotary.tensor_specs())
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        n, h = self.names, self.heads
+        stacked = [tensors[n.q_down], tensors[n.kv_down]] + ([tensors[n.gate]] if n.gate else [])
+        self.w_in = matrix_to(torch.cat(stacked, dim=0), device, dtype)
+        self.w_uq = matrix_to(tensors[n.q_up], device, dtype)
+        # per head W_uk^T [kv_rank, dim]: carries a query head into the latent space
+        self.w_qk = matrix_to(tensors[n.k_up].view(h, self.dim, self.kv_rank).transpose(1, 2), device, dtype)
+        self.w_uv = matrix_to(tensors[n.v_up].view(h, self.vdim, self.kv_rank), device, dtype)
+        self.w_o = matrix_to(tensors[n.o], device, dtype)
+        self.q_norm, self.kv_norm = scale_to(tensors[n.q_norm], device), scale_to(tensors[n.kv_norm], device)
+        self.sink = scale_to(tensors[n.sink], device) if n.sink else None
+        if self.rotary is not None:
+            self.rotary.load(tensors, device, dtype)
+
+    def forward(self, ctx, cache, x: torch.Tensor) -> torch.Tensor:
+        batch = ctx.paged[cache.group]
+        rows, h = x.shape[0], self.heads
+        rotary = self.rotary.fused_rotary() if self.rotary is not None else None
+        inv_freq, rotary_dim = (rotary.inv_freq, rotary.rotary_dim) if rotary is not None else (None, 0)
+        # one product for the two down-projections and the gate's logits
+        proj = ops.linear(x, self.w_in, error_word=ctx.error_word)
+        q_latent = torch.empty((rows, self.q_rank), dtype=x.dtype, device=x.device)
+        ops.latent_prepare(proj, self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm, self.eps,
+                           ctx.positions, inv_freq, rotary_dim, q_latent, cache.k_pool if cache.writable else None,
+                           batch.slots if cache.writable else None, ctx.error_word)
+        q = ops.linear(q_latent, self.w_uq, error_word=ctx.error_word).view(rows, h, self.dim + self.rot_dim)
+        # queries in the cache's own space: [W_uk^T q_plain | rotated part]
+        q_row = torch.empty((rows, h, self.row_width), dtype=x.dtype, device=x.device)
+        ops.head_linear(q, self.w_qk, q_row)
+        if self.rot_dim:
+            ops.rope_slice(q, self.dim, q_row, self.kv_rank, self.rot_dim, rotary_dim, ctx.positions, inv_freq)
+        mixed = torch.empty((rows, h, self.kv_rank), dtype=x.dtype, device=x.device)
+        for launch in batch.launches:
+            b, e = launch.begin, launch.end
+            ops.paged_attention(q_row[b:e], cache.k_pool, None, mixed[b:e], ctx.positions[b:e], ctx.row_request[b:e],
+                                batch.block_table, scale=self.scale, window=0, split_size=launch.split_size,
+                                max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
+                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word, sinks=self.sink)
+        out = torch.empty((rows, h, self.vdim), dtype=x.dtype, device=x.device)
+        gate = proj[:, self.q_rank + self.row_width:] if self.names.gate else None
+        ops.head_linear(mixed, self.w_uv, out, gate=gate)
+        return ops.linear(out.view(rows, h * self.vdim), self.w_o, error_word=ctx.error_word)

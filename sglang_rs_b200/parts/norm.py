@@ -12,7 +12,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import ops
-from .base import Norm, TensorSpec, scale_to
+from .base import Norm, NormedDelta, TensorSpec, scale_to
 
 
 class RmsNorm(Norm):
@@ -28,6 +28,9 @@ class RmsNorm(Norm):
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.weight = scale_to(tensors[self.weight_name], device)
 
+    def spec(self):
+        return ("rms", self.weight, None, self.eps)
+
     def native_record(self):
         """This norm for the step executor: its scale, eps and width."""
         from ..ops.records import SxNorm
@@ -42,3 +45,48 @@ class RmsNorm(Norm):
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, row_index=row_index,
                         write_residual=row_index is None)
         return out
+
+
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b, eps inside the root, all in 32-bit.
+
+    ``add_norm`` takes the pending term as a tensor (added as it is) or as a :class:`NormedDelta` (its own
+    norm is applied first, of either kind), adds it to the residual stream and returns this norm of the sum:
+    one kernel for "norm behind a sublayer, residual sum, norm ahead of the next sublayer"."""
+    graph_safe = True
+    kind = "layer"
+
+    def __init__(self, width: int, eps: float, weight_name: str, bias_name: Optional[str]):
+        self.width, self.eps, self.weight_name, self.bias_name = int(width), float(eps), weight_name, bias_name
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = {self.weight_name: TensorSpec((self.width,), "scale")}
+        if self.bias_name:
+            specs[self.bias_name] = TensorSpec((self.width,))
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        self.weight = scale_to(tensors[self.weight_name], device)
+        self.bias = scale_to(tensors[self.bias_name], device) if self.bias_name else None
+
+    def spec(self):
+        return ("layer", self.weight, self.bias, self.eps)
+
+    def add_norm(self, residual: torch.Tensor, delta, out_dtype: torch.dtype,
+                 row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+        rows = residual.shape[0] if row_index is None else row_index.numel()
+        out = torch.empty((rows, self.width), dtype=out_dtype, device=residual.device)
+        add_pending(residual, delta, self.spec(), out, row_index)
+        return out
+
+
+def add_pending(residual: torch.Tensor, delta, outer, out: Optional[torch.Tensor],
+                row_index: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None) -> None:
+    """residual += delta (a tensor, a :class:`NormedDelta` or None), then ``out`` = ``outer`` of the sum."""
+    inner = None
+    if isinstance(delta, NormedDelta):
+        inner, delta = delta.norm.spec(), delta.values
+    ops.norm_add_norm(residual, delta, inner, outer, out, row_index=row_index, write_residual=row_index is None,
+                      extra=extra)
