@@ -31,11 +31,12 @@ def rms_norm(x, weight, eps):
 
 def rotate_half_split(v, positions, base, dims):
     """Rotates the first ``dims`` entries of the last axis: entry i pairs with entry i + dims/2,
-    angle = position * base^(-2i/dims)."""
+    angle = position * base^(-2i/dims).  The design takes positions and angles in 32-bit: the frequency
+    and the product are rounded to float32, the cosine and sine are those of that angle."""
     half = dims // 2
     i = torch.arange(half, dtype=F)
     freq = torch.pow(torch.tensor(float(base), dtype=F), -2.0 * i / dims)
-    angle = positions.to(F)[:, None] * freq[None, :]                  # [tokens, half]
+    angle = (positions.to(torch.float32)[:, None] * freq.to(torch.float32)[None, :]).to(F)     # [tokens, half]
     while angle.dim() < v.dim():
         angle = angle.unsqueeze(1)
     cos, sin = torch.cos(angle), torch.sin(angle)
