@@ -31,6 +31,7 @@ from __future__ import annotations
 import argparse
 import gc
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -155,7 +156,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel"))
     parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
@@ -178,6 +179,9 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+
+    if args.mode == "gegepel":
+        return gegepel_beside_qwen3(args, warmup)
 
     if args.mode == "timeline":
         # the kernels of a decode step, built with marks that record when each block starts, stops waiting for the
@@ -791,6 +795,96 @@ def serve(args, config, peak, shape_note, warmup) -> int:
 
 
 # ---------------------------------------------------------------------------------------- kernel classes
+#: layers of the size of a real model of each design, at equal width: attention through latents with routed experts
+#: (sizes of the kind that small public models of that family have) beside the Qwen3-1.7B shape
+GEGEPEL_WIDTH = 2048
+GEGEPEL_MIXER = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 512,
+                 "scale": 1.0 / math.sqrt(192), "rot": {"base": 10000.0, "dims": 64}}
+GEGEPEL_MLP = {"kind": "moe", "router": {"experts": 64, "top": 6}, "expert": {"ff": 1408}}
+
+
+def gegepel_beside_qwen3(args, warmup) -> int:
+    """``--mode gegepel``: prefill and decode of a Gegepel model with layers of a real model's size (random weights),
+    beside the Qwen3 shape of equal width, both through the step function: device time per step, tokens per second,
+    and the device time per kernel class of an uncaptured step (CUDA events around every op)."""
+    import torch
+    from sglang_rs_b200.engine.engine import Engine
+    from sglang_rs_b200.engine.runner import StepEntry
+    from sglang_rs_b200.ops import trace
+    layers = args.layers if args.layers is not None else 4
+    vocab = 32768
+    block = {"type": "latent_attention", "mixer": GEGEPEL_MIXER, "mlp": GEGEPEL_MLP}
+    designs = {
+        "gegepel": {"architecture": "Gegepel", "vocab": vocab, "width": GEGEPEL_WIDTH, "embedding": {"scale": 1.0},
+                    "norm": {"eps": 1e-5}, "layers": [block] * layers,
+                    "loop": {"start": 1, "stop": min(3, layers), "times": 2} if layers >= 2 else None},
+        "qwen3": {**model_config("qwen3-1.7b", layers, 1 << 16), "vocab_size": vocab},
+    }
+    peak, source = peaks()
+    length, batch, context = args.prefill_tokens, args.batch, args.context
+    out = {"mode": "gegepel", "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+           "config": {"layers": layers, "width": GEGEPEL_WIDTH, "vocab": vocab, "prefill_tokens": length, "global_batch": batch,
+                      "seq_len": context, "gegepel_mixer": GEGEPEL_MIXER, "gegepel_mlp": GEGEPEL_MLP,
+                      "layer_runs": {"gegepel": layers + (min(3, layers) - 1 if layers >= 2 else 0), "qwen3": layers}},
+           "peaks": {"source": source, **{k: peak[k] for k in ("hbm_gbs", "bf16_tflops") if k in peak}}}
+    for name, document in designs.items():
+        torch.manual_seed(0)
+        tokens = batch * (context + 4 * (args.steps + warmup) + 64) + length + 4096
+        engine = Engine(config=document, random_weights=True, seed=0, dtype="bfloat16", page_size=16, max_total_tokens=tokens,
+                        max_running_requests=batch + 1, chunked_prefill_size=max(2048, length), disable_radix_cache=True)
+        g = torch.Generator().manual_seed(1)
+        prompt = torch.randint(0, vocab, (length,), generator=g).tolist()
+        contexts = torch.randint(0, vocab, (batch, context), generator=g).tolist()
+        result = {}
+
+        def timed(step, repeats):
+            times = []
+            for i in range(warmup + repeats):
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                begin.record()
+                step(i)
+                end.record()
+                torch.cuda.synchronize()
+                if i >= warmup:
+                    times.append(begin.elapsed_time(end))
+            return min(times), statistics.median(times)
+
+        def prefill_step(i):
+            handle = engine.cache.open(f"p{name}{i}-{len(engine.cache.live)}")
+            engine.runner.step([StepEntry(handle, prompt, [length - 1])])
+            engine.cache.close(handle)
+        best, median = timed(prefill_step, 3)
+        result["prefill"] = {"ms": round(best, 3), "ms_median": round(median, 3), "tokens_per_s": round(length / best * 1e3)}
+        handles = [engine.cache.open(f"d{name}{i}") for i in range(batch)]
+        for handle, tokens_of in zip(handles, contexts):
+            for first in range(0, context, 2048):
+                engine.runner.step([StepEntry(handle, tokens_of[first:first + 2048], [])])
+        best, median = timed(lambda i: engine.runner.step([StepEntry(h, [1], [0]) for h in handles]), args.steps)
+        result["decode"] = {"ms": round(best, 4), "ms_median": round(median, 4), "tokens_per_s": round(batch / median * 1e3),
+                            "captured": engine.runner.last_stats.captured}
+        # per kernel class, uncaptured
+        graphs, engine.runner.graphs = engine.runner.graphs, None
+        for kind, step in (("prefill", prefill_step), ("decode", lambda i: engine.runner.step([StepEntry(h, [1], [0]) for h in handles]))):
+            totals = []
+            for i in range(warmup + 3):
+                if i == warmup:
+                    trace.configure("events")
+                step(100 + i)
+                if i >= warmup:
+                    totals.append(dict(engine.runner.last_stats.kernels))
+            trace.configure(None)
+            keys = sorted({k for t in totals for k in t})
+            result[kind]["kernel_ms"] = {k: round(min(t.get(k, 0.0) for t in totals), 4) for k in keys}
+        engine.runner.graphs = graphs
+        for handle in handles:
+            engine.cache.close(handle)
+        out[name] = result
+        del engine
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def kernel_classes(args, config, make_engine, prompts, shape_note, warmup) -> int:
     """Device time per kernel class (CUDA events around every op) of one prefill step of 2,048 tokens and of one
     decode step at ``--batch`` and ``--context``, both uncaptured."""

@@ -13,6 +13,7 @@
 // pairs entry i with entry i + dims/2 of the slice ("rotate half"): (u, v) -> (u cos a - v sin a,
 // v cos a + u sin a), a = position * inv_freq[i]; entries of the slice behind `rotary_dim` pass unchanged.
 #include "common.cuh"
+#include "tile_mma.cuh"
 #include <math.h>
 
 SRB_DEFINE_LAST_ERROR()
@@ -206,6 +207,39 @@ head_linear_kernel(const T* __restrict__ x, size_t x_row, size_t x_head, const T
   }
 }
 
+// The same on the tensor cores (bfloat16): tile_mma.cuh.
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t x_head, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ out, size_t out_row, size_t out_head, int rows, int n_in, int n_out,
+                       const __nv_bfloat16* __restrict__ gate, size_t gate_row) {
+  __shared__ __align__(16) TileMmaSmem s;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int head = blockIdx.z, row0 = blockIdx.y * TM_TILE, col0 = blockIdx.x * TM_TILE;
+  const int t = threadIdx.x;
+  if (t < TM_TILE) s.a_row[t] = row0 + t < rows ? x + (size_t)(row0 + t) * x_row + (size_t)head * x_head : nullptr;
+  __syncthreads();
+  const __nv_bfloat16* const bases[1] = {w + (size_t)head * n_out * n_in + (size_t)col0 * n_in};
+  float acc[1][2][4][4];
+  tile_mma_64x64<1>(s, bases, n_out - col0, n_in, acc);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2) {
+      const int r = row0 + tile_mma_row(i, c2 * 2);
+      if (r >= rows) continue;
+      float g = 1.f;
+      if (gate) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + head])));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c1 = 0; c1 < 2; ++c1) {
+          const int col = col0 + tile_mma_col(j, c1);
+          if (col < n_out) out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
+        }
+    }
+}
+
 // x: rows x_row elements apart, heads x_head apart; w: [heads, n_out, n_in]; out likewise by out_row / out_head.
 // gate (optional): gate[r * gate_row + h] is a logit; the head's result is multiplied by its sigmoid.
 extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head, const void* w, void* out,
@@ -221,7 +255,7 @@ extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head,
                              (size_t)x_head, (const float*)w, (float*)out, (size_t)out_row, (size_t)out_head, rows, n_in,
                              n_out, (const float*)gate, (size_t)gate_row));
   else if (dtype == SRB_DTYPE_BF16)
-    SRB_CUDA_CALL(srb_launch(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, s, (const __nv_bfloat16*)x,
+    SRB_CUDA_CALL(srb_launch(head_linear_mma_kernel, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                              (size_t)x_row, (size_t)x_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (size_t)out_row,
                              (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row));
   else

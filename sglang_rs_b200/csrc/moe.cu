@@ -16,6 +16,7 @@
 // result depends neither on the slot it got nor on the rows beside it.
 #include "common.cuh"
 #include "activations.cuh"
+#include "tile_mma.cuh"
 #include <math.h>
 
 SRB_DEFINE_LAST_ERROR()
@@ -244,12 +245,71 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
   }
 }
 
+// The same tile on the tensor cores (bfloat16): tile_mma.cuh.
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
+                       const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
+                       const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
+                       __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f) {
+  __shared__ __align__(16) TileMmaSmem s;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* tiles = plan + 1 + experts + 1;
+  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
+  const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  const int t = threadIdx.x;
+  if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
+  __syncthreads();
+  const int col0 = blockIdx.x * MOE_TILE;
+  const size_t matrix = (size_t)expert * n_out * n_in + (size_t)col0 * n_in;
+  constexpr int NW = GATED ? 2 : 1;
+  float acc[NW][2][4][4];
+  if (GATED) {
+    const __nv_bfloat16* const bases[2] = {w_a + matrix, w_b + matrix};
+    tile_mma_64x64<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, n_in, acc);
+  } else {
+    const __nv_bfloat16* const bases[2] = {w_a + matrix, nullptr};
+    tile_mma_64x64<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, n_in, acc);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = tile_mma_row(i, c), col = col0 + tile_mma_col(j, c);
+        if (r >= count || col >= n_out) continue;
+        const size_t at = ((size_t)first + r) * n_out + col;
+        if (GATED)
+          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c]));
+        else
+          out_f[at] = acc[0][i][j][c];
+      }
+}
+
 template <typename T>
 static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
                                const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
                                void* out_t, float* out_f, cudaStream_t s) {
   dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts));
   if (grid.y > 65535) SRB_FAIL("moe product: %d tiles exceed one launch", (int)grid.y);
+  if (sizeof(T) == 2) {
+    // bfloat16: the tensor cores
+    if (gated)
+      SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
+                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
+                               activation, (__nv_bfloat16*)out_t, out_f));
+    else
+      SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
+                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
+                               activation, (__nv_bfloat16*)out_t, out_f));
+    SRB_LAUNCH_CHECK("moe product");
+    return SRB_OK;
+  }
   if (gated)
     SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, true>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
                              plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f));

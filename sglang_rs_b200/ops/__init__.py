@@ -427,6 +427,55 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 
 
+def latent_attention_takes(dtype: torch.dtype, row_dim: int, value_dim: int) -> bool:
+    """True if the tensor-core kernel for attention over rows that are key and value takes these sizes (the rule of
+    srb_latent_attention_supports, asked here so that other models never compile it)."""
+    return (dtype == torch.bfloat16 and row_dim % 16 == 0 and value_dim % 32 == 0 and 0 < value_dim <= min(row_dim, 512))
+
+
+@traced("attention_latent")
+def latent_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+                     row_request: torch.Tensor, block_table: torch.Tensor, *, scale: float, sinks: Optional[torch.Tensor],
+                     error_word: torch.Tensor, tiles: Optional[torch.Tensor] = None, split_size: int = 0, max_splits: int = 1,
+                     scratch_acc: Optional[torch.Tensor] = None, scratch_ml: Optional[torch.Tensor] = None) -> None:
+    """Attention of ``n_q`` query heads over cache rows that are key (the whole row) and value (its first
+    ``out.shape[2]`` entries), bfloat16 on the tensor cores, with an optional sink per head.
+
+    With ``tiles`` (int32 [n, 4]: first row, rows <= 64, request, first position) the rows of the tiles are prompt
+    portions: every row sees the keys up to its own position, and rows outside the tiles are left untouched.  Without,
+    every row of ``q`` is one decoded token whose keys are cut every ``split_size`` positions (a multiple of 64); partial
+    results go through the scratch tensors (rows * n_q * max_splits * value_dim and rows * n_q * max_splits * 2 floats)."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "pool", torch.bfloat16)
+    _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    rows, n_q, row_dim = q.shape
+    num_pages, kv_heads, page_size, pool_dim = pool.shape
+    value_dim = out.shape[2]
+    if kv_heads != 1 or pool_dim != row_dim or out.shape[:2] != q.shape[:2] or not latent_attention_takes(q.dtype, row_dim, value_dim):
+        raise KernelError("latent_attention: shapes of q, out and the pool do not agree or are not taken")
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_q:
+            raise KernelError("latent_attention: one sink per query head is needed")
+    num_tiles = 0
+    if tiles is not None:
+        _need(tiles, "tiles", torch.int32)
+        if tiles.shape[-1] != 4:
+            raise KernelError("latent_attention: tiles must be [n, 4]")
+        num_tiles, split_size, max_splits = tiles.shape[0], 0, 1
+    else:
+        need_acc, need_ml = attention_scratch_sizes(rows, n_q, value_dim, max_splits)
+        if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
+            raise KernelError("latent_attention: scratch tensors are too small for this split run")
+        _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
+    lib = load_library("attention_latent")
+    _check(lib, lib.srb_latent_attention(
+        _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions), _ptr(row_request),
+        _ptr(block_table), block_table.stride(0), rows, n_q, row_dim, value_dim, page_size, num_pages, int(split_size),
+        int(max_splits), _ptr(tiles), num_tiles, ctypes.c_float(scale), _ptr(sinks), _ptr(error_word), _stream()),
+        launches=1 if tiles is not None else 2)
+
+
 #: the most blocks per (row, kv head) that :func:`decode_splits` ever returns
 DECODE_MAX_SPLITS = 64
 
@@ -551,7 +600,7 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
 
 # --------------------------------------------------------------------------- latents and per-head products
 
-@traced("rope_kv")
+@traced("latent_prepare")
 def latent_prepare(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
                    kv_weight: torch.Tensor, eps: float, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
                    rotary_dim: int, q_latent: Optional[torch.Tensor], pool: Optional[torch.Tensor],
@@ -586,7 +635,7 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, 
         ctypes.c_longlong(pool_rows), _ptr(error_word), dtype_code(proj.dtype), _stream()))
 
 
-@traced("rope_kv")
+@traced("rope_slice")
 def rope_slice(x: torch.Tensor, in_offset: int, out: torch.Tensor, out_offset: int, width: int, rotary_dim: int,
                positions: torch.Tensor, inv_freq: Optional[torch.Tensor]) -> None:
     """out[r, h, out_offset + i] = rotated(x[r, h, in_offset + i]), i < width, pairs (i, i + rotary_dim / 2);
@@ -607,7 +656,7 @@ def rope_slice(x: torch.Tensor, in_offset: int, out: torch.Tensor, out_offset: i
         rotary_dim, _ptr(positions), _ptr(inv_freq), dtype_code(x.dtype), _stream()))
 
 
-@traced("gemm")
+@traced("head_linear")
 def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
     """out[r, h, :n_out] = weight[h] @ x[r, h, :n_in] with ``weight`` [heads, n_out, n_in]; x and out are views
     [rows, heads, >= n] with a dense last axis.  ``gate`` ([rows, >= heads] view of logits): head h's result is
@@ -631,7 +680,7 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
 
 # --------------------------------------------------------------------------- routed experts
 
-@traced("gemm")
+@traced("routed_experts")
 def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
                    top: int, activation: str, renormalize: bool, error_word: torch.Tensor) -> torch.Tensor:
     """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].

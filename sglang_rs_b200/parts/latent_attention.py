@@ -124,8 +124,20 @@ class LatentAttention(Mixer):
         if self.rot_dim:
             ops.rope_slice(q, self.dim, q_row, self.kv_rank, self.rot_dim, rotary_dim, ctx.positions, inv_freq)
         mixed = torch.empty((rows, h, self.kv_rank), dtype=x.dtype, device=x.device)
+        tensor_cores = ops.latent_attention_takes(x.dtype, self.row_width, self.kv_rank)
         for launch in batch.launches:
             b, e = launch.begin, launch.end
+            if tensor_cores and launch.tiles is not None:
+                # prompt portions: the tiles name their rows of the whole step
+                ops.latent_attention(q_row, cache.k_pool, mixed, ctx.positions, ctx.row_request, batch.block_table,
+                                     scale=self.scale, sinks=self.sink, error_word=ctx.error_word, tiles=launch.tiles)
+                continue
+            if tensor_cores and launch.split_size and launch.split_size % 64 == 0:
+                ops.latent_attention(q_row[b:e], cache.k_pool, mixed[b:e], ctx.positions[b:e], ctx.row_request[b:e],
+                                     batch.block_table, scale=self.scale, sinks=self.sink, error_word=ctx.error_word,
+                                     split_size=launch.split_size, max_splits=launch.max_splits,
+                                     scratch_acc=batch.scratch_acc, scratch_ml=batch.scratch_ml)
+                continue
             ops.paged_attention(q_row[b:e], cache.k_pool, None, mixed[b:e], ctx.positions[b:e], ctx.row_request[b:e],
                                 batch.block_table, scale=self.scale, window=0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,

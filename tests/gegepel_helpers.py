@@ -55,6 +55,15 @@ SMALL_C = config(64, 80, [
 ], loop=(1, 2, 3), scale=2.0)
 
 
+#: sizes that the tensor-core kernels of the bfloat16 path take in every layer (rows of 80 and 48 entries, values of 64
+#: and 32), fewer heads than a block of the attention kernel has slots, and more
+SMALL_D = config(64, 90, [
+    layer(mixer(5, 16, 16, 24, 32, 64), moe(6, 2, 48)),
+    layer(mixer(20, 8, 16, 8, 24, 32, rot_dims=8), moe(3, 2, 16)),
+    layer(mixer(2, 32, 16, 16, 40, 64), None),
+], loop=(1, 3, 2), scale=1.3)
+
+
 def make_folder(tmp_path, name: str, doc: dict, seed: int, dtype: torch.dtype, sharpen: float = 3.0) -> str:
     """A model folder from the engine's random-weights mode, changed so that faults show: the query latent's
     scale is multiplied by ``sharpen`` (peaked attention), sinks are spread (a sink that is left out or counted
@@ -114,7 +123,7 @@ def far_key_folder(tmp_path, dtype: torch.dtype) -> str:
     there, which the query latent reads and head 0's rotated query part gets in the same pair.  The score of that key is
     then far above all others, and the logits of later positions depend on it."""
     from sglang_rs_b200.weights import read_model_dir, write_file
-    doc = config(48, 60, [layer(mixer(2, 16, 8, 16, 24, 24, base=10000.0), moe(3, 1, 16))], scale=1.0)
+    doc = config(48, 60, [layer(mixer(2, 16, 16, 16, 24, 32, base=10000.0), moe(3, 1, 16))], scale=1.0)
     folder = make_folder(tmp_path, "far", doc, seed=7, dtype=dtype)
     t = {k: v.float().clone() for k, v in read_model_dir(folder).items()}
     m = doc["layers"][0]["mixer"]

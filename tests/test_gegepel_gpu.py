@@ -160,6 +160,71 @@ def test_attention_over_shared_rows_with_a_sink(dtype, heads, split):
     assert int(word.item()) == 0
 
 
+@pytest.mark.parametrize("heads,width,value_dim", [(3, 48, 32), (8, 80, 64), (16, 144, 96), (34, 32, 32)])
+def test_tensor_core_attention_over_shared_rows(heads, width, value_dim):
+    """The bfloat16 kernel for rows that are key and value: prompt portions given as tiles (several requests, a portion
+    that starts in the middle of a page and of a 64-key block, rows outside the tiles untouched) and decoded rows whose
+    keys are split; one head looks at a single far key."""
+    from sglang_rs_b200 import ops
+    torch.manual_seed(6)
+    dtype, page = torch.bfloat16, 8
+    lengths = [150, 70]                                     # two requests; their last 41 and 70 tokens are this step's rows
+    portions = [(0, 109, 41), (1, 0, 70)]                   # (request, first position, rows)
+    keys = [torch.randn(n, width) for n in lengths]
+    rows = sum(n for _, _, n in portions)
+    q = torch.randn(rows + 2, heads, width)                 # two rows behind the portions that no tile names
+    keys[0][5] = 5.0 * q[40, 0] / q[40, 0].norm()           # the last row of request 0, head 0, looks at key 5
+    sinks = torch.randn(heads) * 2
+    pages = torch.randperm(40)
+    pool = torch.zeros((40, 1, page, width), dtype=dtype, device=DEV)
+    table = torch.full((2, 24), -1, dtype=torch.int32)
+    used = 0
+    for r, k in enumerate(keys):
+        for pos in range(len(k)):
+            if pos % page == 0:
+                table[r, pos // page] = pages[used]
+                used += 1
+            pool[table[r, pos // page], 0, pos % page] = k[pos].to(dtype)
+    tiles, positions, row_request, first = [], [], [], 0
+    for request, start, count in portions:
+        for offset in range(0, count, 64):
+            tiles.append([first + offset, min(64, count - offset), request, start + offset])
+        positions += list(range(start, start + count))
+        row_request += [request] * count
+        first += count
+    positions += [0, 0]
+    row_request += [0, 0]
+    word = ops.new_error_word(DEV)
+    out = torch.full((rows + 2, heads, value_dim), 7.0, dtype=dtype, device=DEV)
+    ops.latent_attention(q.to(DEV, dtype), pool, out, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                         torch.tensor(row_request, dtype=torch.int32, device=DEV), table.to(DEV), scale=0.25, sinks=sinks.to(DEV),
+                         error_word=word, tiles=torch.tensor(tiles, dtype=torch.int32, device=DEV))
+
+    def plain(row):
+        k = seen(keys[row_request[row]], dtype)[:positions[row] + 1]
+        scores = torch.einsum("hd,jd->hj", seen(q, dtype)[row], k) * 0.25
+        w = pg.softmax_with_sink(scores[:, None, :], sinks.double())[:, 0]
+        return w, w @ k[:, :value_dim]
+    for row in range(rows):
+        w, want = plain(row)
+        close(out[row], want, dtype, f"portion row {row}")
+        if row == 40:
+            assert float(w[0, 5]) > 0.5
+    assert float((out[rows:] - 7.0).abs().max()) == 0 and int(word.item()) == 0
+    # the same rows as decoded tokens, keys cut every 64 positions
+    picks = [40, 0, rows - 1, 41]
+    splits = 3
+    acc = torch.empty(len(picks) * heads * splits * value_dim, device=DEV)
+    ml = torch.empty(len(picks) * heads * splits * 2, device=DEV)
+    single = torch.empty((len(picks), heads, value_dim), dtype=dtype, device=DEV)
+    ops.latent_attention(q[picks].to(DEV, dtype), pool, single, torch.tensor([positions[r] for r in picks], dtype=torch.int32, device=DEV),
+                         torch.tensor([row_request[r] for r in picks], dtype=torch.int32, device=DEV), table.to(DEV), scale=0.25,
+                         sinks=sinks.to(DEV), error_word=word, split_size=64, max_splits=splits, scratch_acc=acc, scratch_ml=ml)
+    for i, row in enumerate(picks):
+        close(single[i], plain(row)[1], dtype, f"decoded row {row}")
+    assert int(word.item()) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,rows", [(5, 2, 150), (3, 3, 9), (4, 1, 1), (70, 4, 40)])
 def test_routed_experts(dtype, experts, top, rows):
@@ -190,7 +255,7 @@ def test_routed_experts(dtype, experts, top, rows):
 
 # ------------------------------------------------------------------------------ whole models, every way of cutting
 @pytest.mark.parametrize("dtype_name,stored,tolerance", DTYPES)
-@pytest.mark.parametrize("doc", [gh.SMALL_A, gh.SMALL_B, gh.SMALL_C], ids=["a", "b", "c"])
+@pytest.mark.parametrize("doc", [gh.SMALL_A, gh.SMALL_B, gh.SMALL_C, gh.SMALL_D], ids=["a", "b", "c", "d"])
 def test_prompts_tails_portions_and_mixed_batches(tmp_path, doc, dtype_name, stored, tolerance):
     folder = gh.make_folder(tmp_path, "m", doc, seed=5, dtype=stored)
     requests = gh.random_requests(doc, (1, 2, 23, 64, 65, 150, 131), seed=3)
