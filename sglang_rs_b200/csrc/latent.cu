@@ -240,6 +240,40 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t
     }
 }
 
+// Tiles of 128 rows with operands through a ring of asynchronous copies, for rows on 16-byte boundaries.
+__global__ void __launch_bounds__(256)
+head_linear_async_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t x_head, const __nv_bfloat16* __restrict__ w,
+                         __nv_bfloat16* __restrict__ out, size_t out_row, size_t out_head, int rows, int n_in, int n_out,
+                         const __nv_bfloat16* __restrict__ gate, size_t gate_row) {
+  extern __shared__ __align__(16) unsigned char hl_smem[];
+  TileAsyncSmem<1>& s = *reinterpret_cast<TileAsyncSmem<1>*>(hl_smem);
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int head = blockIdx.z, row0 = blockIdx.y * TA_ROWS, col0 = blockIdx.x * TA_COLS;
+  const int t = threadIdx.x;
+  if (t < TA_ROWS) s.a_row[t] = row0 + t < rows ? x + (size_t)(row0 + t) * x_row + (size_t)head * x_head : nullptr;
+  __syncthreads();
+  const __nv_bfloat16* const bases[1] = {w + (size_t)head * n_out * n_in + (size_t)col0 * n_in};
+  float acc[1][2][4][4];
+  tile_mma_128x64_async<1>(s, bases, n_out - col0, rows - row0, n_in, acc);
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2) {
+      const int r = row0 + tile_async_row(i, c2 * 2);
+      if (r >= rows) continue;
+      float g = 1.f;
+      if (gate) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + head])));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c1 = 0; c1 < 2; ++c1) {
+          const int col = col0 + tile_async_col(j, c1);
+          if (col < n_out) out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
+        }
+    }
+}
+
 // x: rows x_row elements apart, heads x_head apart; w: [heads, n_out, n_in]; out likewise by out_row / out_head.
 // gate (optional): gate[r * gate_row + h] is a logit; the head's result is multiplied by its sigmoid.
 extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head, const void* w, void* out,
@@ -254,7 +288,15 @@ extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head,
     SRB_CUDA_CALL(srb_launch(head_linear_kernel<float>, grid, dim3(256), 0, s, (const float*)x, (size_t)x_row,
                              (size_t)x_head, (const float*)w, (float*)out, (size_t)out_row, (size_t)out_head, rows, n_in,
                              n_out, (const float*)gate, (size_t)gate_row));
-  else if (dtype == SRB_DTYPE_BF16)
+  else if (dtype == SRB_DTYPE_BF16 && n_in % 8 == 0 && x_row % 8 == 0 && x_head % 8 == 0 &&
+           (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    grid.y = (rows + TA_ROWS - 1) / TA_ROWS;
+    SRB_CUDA_CALL(cudaFuncSetAttribute(head_linear_async_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)sizeof(TileAsyncSmem<1>)));
+    SRB_CUDA_CALL(srb_launch(head_linear_async_kernel, grid, dim3(256), sizeof(TileAsyncSmem<1>), s, (const __nv_bfloat16*)x,
+                             (size_t)x_row, (size_t)x_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (size_t)out_row,
+                             (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row));
+  } else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(head_linear_mma_kernel, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                              (size_t)x_row, (size_t)x_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (size_t)out_row,
                              (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row));

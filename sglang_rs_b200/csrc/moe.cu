@@ -22,7 +22,8 @@
 SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
 
-#define MOE_TILE 64      // rows of a tile, and output columns of a block
+#define MOE_ROWS 128     // rows of a tile of the plan: slots of one expert that one block (or two) takes
+#define MOE_TILE 64      // rows that the smaller kernels take at a time (half a tile), and output columns of a block
 #define MOE_K 16
 #define MOE_MAX_EXPERTS 1024
 
@@ -35,12 +36,40 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const T* __restrict__ 
   srb_grid_dependency_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const T* x = h + (size_t)row * width;
-  for (int e = warp; e < experts; e += warps) {
-    const T* w = router + (size_t)e * width;
-    float partial = 0.f;
-    for (int i = lane; i < width; i += 32) partial += srb_to_float(x[i]) * srb_to_float(w[i]);
-    partial = srb_warp_sum(partial);
-    if (lane == 0) score[e] = partial;
+  if (sizeof(T) == 2 && width % 8 == 0 && (((uintptr_t)h | (uintptr_t)router) & 15) == 0) {
+    // 16-byte loads: a lane's pieces of the row stay in registers for every expert of its warp (up to 4 pieces:
+    // widths to 1024; wider rows read the later pieces again per expert)
+    const int pieces = width / 8;
+    uint4 mine[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      mine[j] = lane + 32 * j < pieces ? *reinterpret_cast<const uint4*>(x + (size_t)(lane + 32 * j) * 8) : make_uint4(0u, 0u, 0u, 0u);
+    for (int e = warp; e < experts; e += warps) {
+      const T* w = router + (size_t)e * width;
+      float partial = 0.f;
+      for (int piece = lane, j = 0; piece < pieces; piece += 32, ++j) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + (size_t)piece * 8);
+        const uint4 xv = j < 4 ? mine[j < 4 ? j : 0] : *reinterpret_cast<const uint4*>(x + (size_t)piece * 8);
+        const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 a = __bfloat1622float2(x2[q]), b = __bfloat1622float2(w2[q]);
+          partial = fmaf(a.x, b.x, partial);
+          partial = fmaf(a.y, b.y, partial);
+        }
+      }
+      partial = srb_warp_sum(partial);
+      if (lane == 0) score[e] = partial;
+    }
+  } else {
+    for (int e = warp; e < experts; e += warps) {
+      const T* w = router + (size_t)e * width;
+      float partial = 0.f;
+      for (int i = lane; i < width; i += 32) partial += srb_to_float(x[i]) * srb_to_float(w[i]);
+      partial = srb_warp_sum(partial);
+      if (lane == 0) score[e] = partial;
+    }
   }
   __syncthreads();
   if (warp != 0) return;
@@ -120,7 +149,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
       first[e] = slots;
       tile_first[e] = tiles;
       slots += count[e];
-      tiles += (count[e] + MOE_TILE - 1) / MOE_TILE;
+      tiles += (count[e] + MOE_ROWS - 1) / MOE_ROWS;
     }
     first[experts] = slots;
     tile_first[experts] = tiles;
@@ -137,7 +166,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
       const int at = tile_first[e] + t;
       if (at < max_tiles) {
         tiles[2 * at] = e;
-        tiles[2 * at + 1] = first[e] + t * MOE_TILE;
+        tiles[2 * at + 1] = first[e] + t * MOE_ROWS;
       }
     }
     count[e] = 0;                       // becomes the number of the expert's slots handed out so far
@@ -153,11 +182,11 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
 }
 
 extern "C" int srb_moe_plan_ints(int rows, int top, int experts) {
-  const int max_tiles = (rows * top) / MOE_TILE + experts;
+  const int max_tiles = (rows * top) / MOE_ROWS + experts;
   return 1 + experts + 1 + 2 * max_tiles;
 }
 
-extern "C" int srb_moe_max_tiles(int rows, int top, int experts) { return (rows * top) / MOE_TILE + experts; }
+extern "C" int srb_moe_max_tiles(int rows, int top, int experts) { return (rows * top) / MOE_ROWS + experts; }
 
 extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, int* plan, int* slot_row, int* entry_slot,
                             int* error_word, void* stream) {
@@ -169,7 +198,7 @@ extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, i
   return SRB_OK;
 }
 
-// A tile of up to 64 slots of one expert times 64 output columns.  GATED: two weight matrices (gate, up), rows of
+// Half a tile (up to 64 slots of one expert; blockIdx.z names the half) times 64 output columns.  GATED: two weight matrices (gate, up), rows of
 // x gathered through slot_row, result act(gate) * up in T.  Otherwise one matrix, rows of x are the slots
 // themselves, result in float.
 template <typename T, bool GATED>
@@ -187,8 +216,9 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
   if (tile >= plan[0]) return;
   const int* offsets = plan + 1;
   const int* tiles = plan + 1 + experts + 1;
-  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
+  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1] + MOE_TILE * blockIdx.z;
   const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  if (count <= 0) return;
   const int t = threadIdx.x;
   if (t < MOE_TILE) tile_row[t] = t < count ? (GATED ? slot_row[first + t] : first + t) : -1;
   __syncthreads();
@@ -259,8 +289,9 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   if (tile >= plan[0]) return;
   const int* offsets = plan + 1;
   const int* tiles = plan + 1 + experts + 1;
-  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
+  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1] + MOE_TILE * blockIdx.z;
   const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  if (count <= 0) return;
   const int t = threadIdx.x;
   if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
@@ -291,12 +322,90 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
       }
 }
 
+// A whole tile (up to 128 slots) times 64 output columns, operands through a ring of asynchronous copies
+// (tile_mma.cuh); for rows that start on 16-byte boundaries.
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
+                         const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
+                         const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
+                         __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f) {
+  constexpr int NW = GATED ? 2 : 1;
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  TileAsyncSmem<NW>& s = *reinterpret_cast<TileAsyncSmem<NW>*>(moe_smem);
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* tiles = plan + 1 + experts + 1;
+  const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
+  const int count = min(MOE_ROWS, offsets[expert + 1] - first);
+  const int t = threadIdx.x;
+  if (t < MOE_ROWS) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
+  __syncthreads();
+  const int col0 = blockIdx.x * TA_COLS;
+  const size_t matrix = (size_t)expert * n_out * n_in + (size_t)col0 * n_in;
+  float acc[NW][2][4][4];
+  if (GATED) {
+    const __nv_bfloat16* const bases[2] = {w_a + matrix, w_b + matrix};
+    tile_mma_128x64_async<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
+  } else {
+    const __nv_bfloat16* const bases[2] = {w_a + matrix, nullptr};
+    tile_mma_128x64_async<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; c += 2) {
+        const int r = tile_async_row(i, c), col = col0 + tile_async_col(j, c);      // columns col and col + 1
+        if (r >= count || col >= n_out) continue;
+        const size_t at = ((size_t)first + r) * n_out + col;
+        const bool pair = col + 1 < n_out;
+        if (GATED) {
+          const float lo = srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c]);
+          const float hi = srb_gated<true>(activation, acc[0][i][j][c + 1], acc[NW - 1][i][j][c + 1]);
+          if (pair && (at & 1) == 0) {
+            *reinterpret_cast<unsigned*>(out_t + at) = pack_bf16(lo, hi);
+          } else {
+            out_t[at] = __float2bfloat16_rn(lo);
+            if (pair) out_t[at + 1] = __float2bfloat16_rn(hi);
+          }
+        } else if (pair && (at & 1) == 0) {
+          *reinterpret_cast<float2*>(out_f + at) = make_float2(acc[0][i][j][c], acc[0][i][j][c + 1]);
+        } else {
+          out_f[at] = acc[0][i][j][c];
+          if (pair) out_f[at + 1] = acc[0][i][j][c + 1];
+        }
+      }
+}
+
 template <typename T>
 static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
                                const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
                                void* out_t, float* out_f, cudaStream_t s) {
-  dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts));
+  dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts), MOE_ROWS / MOE_TILE);
   if (grid.y > 65535) SRB_FAIL("moe product: %d tiles exceed one launch", (int)grid.y);
+  if (sizeof(T) == 2 && n_in % 8 == 0 && (((uintptr_t)x | (uintptr_t)w_a | (uintptr_t)w_b) & 15) == 0) {
+    // bfloat16 rows on 16-byte boundaries: whole tiles, operands by asynchronous copies
+    grid.z = 1;
+    const size_t smem = gated ? sizeof(TileAsyncSmem<2>) : sizeof(TileAsyncSmem<1>);
+    if (gated) {
+      SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<true>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x,
+                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
+                               activation, (__nv_bfloat16*)out_t, out_f));
+    } else {
+      SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<false>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x,
+                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
+                               activation, (__nv_bfloat16*)out_t, out_f));
+    }
+    SRB_LAUNCH_CHECK("moe product");
+    return SRB_OK;
+  }
   if (sizeof(T) == 2) {
     // bfloat16: the tensor cores
     if (gated)

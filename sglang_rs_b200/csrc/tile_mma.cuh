@@ -104,3 +104,92 @@ __device__ __forceinline__ int tile_mma_row(int i, int c) {
 __device__ __forceinline__ int tile_mma_col(int j, int c) {
   return ((threadIdx.x >> 5) & 1) * 32 + j * 8 + (threadIdx.x & 3) * 2 + (c & 1);
 }
+
+// ---- the same product on a 128 x 64 tile with asynchronous copies ----------------------------------------------
+// For operands whose rows start on 16-byte boundaries (n_in a multiple of 8, aligned bases): 256 threads, warp (wy, wx)
+// of a 4 x 2 grid owns 32 rows x 32 columns as above; K is walked 32 at a time through a ring of three stages that
+// cp.async fills two steps ahead, so a block keeps two steps of operands in flight while it multiplies a third.  A
+// tile of 128 rows reads each weight tile half as often as two tiles of 64 would.
+#define TA_ROWS 128
+#define TA_COLS 64
+#define TA_STAGES 3
+
+template <int NW> struct TileAsyncSmem {
+  __nv_bfloat16 a[TA_STAGES][TA_ROWS][TM_PITCH];
+  __nv_bfloat16 w[TA_STAGES][NW][TA_COLS][TM_PITCH];
+  const __nv_bfloat16* a_row[TA_ROWS];
+};
+
+// rows_valid: rows of the tile that exist; a warp whose 16-row groups lie behind them multiplies nothing (with a few
+// decoded tokens per expert most of the tile is empty, and the products of empty rows would cost more than the copies).
+template <int NW>
+__device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, const __nv_bfloat16* const (&w_base)[NW],
+                                                      int cols_valid, int rows_valid, int n_in, float (&acc)[NW][2][4][4]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wy = warp >> 1, wx = warp & 1;
+#pragma unroll
+  for (int m = 0; m < NW; ++m)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[m][i][j][c] = 0.f;
+  const int steps = (n_in + TM_K - 1) / TM_K;
+  auto issue = [&](int step) {
+    if (step < steps) {
+      const int stage = step % TA_STAGES, k0 = step * TM_K;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                                       // 128 rows x 4 pieces of A
+        const int piece = tid + h * 256, row = piece >> 2, k = k0 + (piece & 3) * 8;
+        const __nv_bfloat16* a = s.a_row[row];
+        const bool there = a != nullptr && k < n_in;
+        cp_async_16(&s.a[stage][row][(piece & 3) * 8], there ? a + k : w_base[0], there ? 16 : 0);
+      }
+#pragma unroll
+      for (int m = 0; m < NW; ++m) {                                      // 64 rows x 4 pieces of each W
+        const int row = tid >> 2, k = k0 + (tid & 3) * 8;
+        const bool there = row < cols_valid && k < n_in;
+        cp_async_16(&s.w[stage][m][row][(tid & 3) * 8], there ? w_base[m] + (size_t)row * n_in + k : w_base[0], there ? 16 : 0);
+      }
+    }
+    cp_async_commit();                                                    // an empty group keeps the count in step
+  };
+#pragma unroll
+  for (int step = 0; step < TA_STAGES - 1; ++step) issue(step);
+  for (int step = 0; step < steps; ++step) {
+    cp_async_wait<TA_STAGES - 2>();                                       // the copies of this step have landed
+    __syncthreads();                                                      // ... for every thread, and the step before is multiplied
+    issue(step + TA_STAGES - 1);                                          // into the stage that was multiplied last
+    const int stage = step % TA_STAGES;
+    if (wy * 32 >= rows_valid) continue;                                  // (the same for all lanes of the warp)
+    const bool second = wy * 32 + 16 < rows_valid;
+#pragma unroll
+    for (int kk = 0; kk < TM_K; kk += 16) {
+      unsigned a[2][4];
+      ldmatrix_x4(a[0][0], a[0][1], a[0][2], a[0][3], &s.a[stage][wy * 32 + (lane & 15)][kk + (lane >> 4) * 8]);
+      if (second) ldmatrix_x4(a[1][0], a[1][1], a[1][2], a[1][3], &s.a[stage][wy * 32 + 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int m = 0; m < NW; ++m)
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3,
+                      &s.w[stage][m][wx * 32 + jj * 16 + (lane & 7) + ((lane >> 4) << 3)][kk + ((lane >> 3) & 1) * 8]);
+          mma_bf16(acc[m][0][2 * jj], a[0], b0, b1);
+          mma_bf16(acc[m][0][2 * jj + 1], a[0], b2, b3);
+          if (second) {
+            mma_bf16(acc[m][1][2 * jj], a[1], b0, b1);
+            mma_bf16(acc[m][1][2 * jj + 1], a[1], b2, b3);
+          }
+        }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+// where element c of acc[..][i][j] lies in the 128 x 64 tile
+__device__ __forceinline__ int tile_async_row(int i, int c) {
+  return ((threadIdx.x >> 5) >> 1) * 32 + i * 16 + ((threadIdx.x & 31) >> 2) + (c >> 1) * 8;
+}
+__device__ __forceinline__ int tile_async_col(int j, int c) { return tile_mma_col(j, c); }

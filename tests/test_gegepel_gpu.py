@@ -110,8 +110,13 @@ def test_latents_rotation_and_cache_rows(dtype):
 def test_one_matrix_per_head_with_a_gate(dtype):
     from sglang_rs_b200 import ops
     torch.manual_seed(3)
-    rows, heads, n_in, n_out = 70, 3, 21, 67
-    x = torch.randn(rows, heads, n_in + 4)
+    for rows, heads, n_in, n_out, spare in ((70, 3, 21, 67, 4), (300, 2, 40, 72, 8)):        # odd sizes; rows on 16-byte borders
+        one_matrix_per_head(dtype, rows, heads, n_in, n_out, spare)
+
+
+def one_matrix_per_head(dtype, rows, heads, n_in, n_out, spare):
+    from sglang_rs_b200 import ops
+    x = torch.randn(rows, heads, n_in + spare)
     w = torch.randn(heads, n_out, n_in)
     gate = torch.randn(rows, heads + 2) * 3
     out = torch.zeros((rows, heads, n_out + 3), dtype=dtype, device=DEV)
@@ -226,7 +231,7 @@ def test_tensor_core_attention_over_shared_rows(heads, width, value_dim):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,rows", [(5, 2, 150), (3, 3, 9), (4, 1, 1), (70, 4, 40)])
+@pytest.mark.parametrize("experts,top,rows", [(5, 2, 150), (3, 3, 9), (4, 1, 1), (70, 4, 40), (3, 2, 500)])
 def test_routed_experts(dtype, experts, top, rows):
     from sglang_rs_b200 import ops
     torch.manual_seed(5)
