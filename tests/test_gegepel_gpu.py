@@ -357,3 +357,44 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype_name, stored)
     engine.cache.check_invariants()
     assert engine.flush_cache()
     assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
+
+
+def test_the_command_line_and_the_trace_program_take_the_design(tmp_path):
+    """`sglang-rs random-model` writes a folder from a configuration, `sglang-rs generate` decodes from it (greedy, and with
+    temperature and top-k from a seed), and `trace_run` replays steps on it: the same programs as for every model."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(gh.SMALL_D))
+    folder = str(tmp_path / "written")
+    made = subprocess.run([sys.executable, os.path.join(root, "bin", "sglang-rs"), "random-model", "--config", str(config_path),
+                           "--out", folder, "--seed", "4", "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert made.returncode == 0, made.stderr[-2000:]
+    doc, tensors = gh.load_folder(folder)
+    command = [sys.executable, os.path.join(root, "bin", "sglang-rs"), "generate", f"--model-path={folder}", "--device", "cuda",
+               "--dtype", "float32", "--input-ids", "5,17,3", "--input-ids", "9 8 7 6", "--max-new-tokens", "5",
+               "--max-total-tokens", "256"]
+    process = subprocess.run(command, capture_output=True, text=True, timeout=600)
+    assert process.returncode == 0, process.stderr[-2000:]
+    lines = [json.loads(line) for line in process.stdout.strip().splitlines()]
+    assert [l["output_ids"] for l in lines] == [gh.plain_greedy(doc, tensors, p, 5) for p in ([5, 17, 3], [9, 8, 7, 6])]
+    sampled = [subprocess.run(command + ["--temperature", "0.9", "--top-k", "8", "--sampling-seed", "3"], capture_output=True,
+                              text=True, timeout=600) for _ in range(2)]
+    assert sampled[0].returncode == 0 and sampled[0].stdout == sampled[1].stdout
+    assert all(0 <= t < doc["vocab"] for line in sampled[0].stdout.strip().splitlines() for t in json.loads(line)["output_ids"])
+    tokens = gh.random_requests(doc, (37,), seed=1)["r0"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:30], "want": [0, 29]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[30:], "want": [6]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    replay = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                             "--out", str(out), "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                            capture_output=True, text=True, timeout=600)
+    assert replay.returncode == 0 and replay.stdout.split() == ["done", "0", "done", "1"], replay.stderr[-2000:]
+    want = pg.forward(doc, tensors, tokens).numpy()
+    first = np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1)
+    last = np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1)
+    for got, pos in ((first[0], 0), (first[1], 29), (last[0], 36)):
+        assert float(np.abs(got - want[pos]).max()) <= 2e-5 * float(np.abs(want).max())

@@ -617,18 +617,23 @@ def test_attention_refuses_sizes_it_cannot_take():
         ops.paged_attention(bad_q, case["k_pool"], case["v_pool"], torch.empty_like(bad_q), case["positions"],
                             case["row_request"], case["table"], scale=1.0, window=0, split_size=0, max_splits=1,
                             scratch_acc=None, scratch_ml=None, error_word=ops.new_error_word(DEV))
-    pool = torch.zeros(4, 1, 16, 520, device=DEV)
-    q = torch.zeros(1, 2, 520, device=DEV)
-    with pytest.raises(ops.KernelError, match="at most 512"):
+    pool = torch.zeros(4, 1, 16, 1040, device=DEV)
+    q = torch.zeros(1, 2, 1040, device=DEV)
+    with pytest.raises(ops.KernelError, match="at most 1024"):
         ops.paged_attention(q, pool, pool, torch.empty_like(q), case["positions"], case["row_request"], case["table"],
                             scale=1.0, window=0, split_size=0, max_splits=1, scratch_acc=None, scratch_ml=None,
                             error_word=ops.new_error_word(DEV))
-    pool = torch.zeros(4, 1, 16, 16, device=DEV)
-    q = torch.zeros(1, 40, 16, device=DEV)
-    with pytest.raises(ops.KernelError, match="exceed 32"):
-        ops.paged_attention(q, pool, pool, torch.empty_like(q), case["positions"], case["row_request"], case["table"],
+    # more than 32 query heads on a kv head go in chunks of heads: the same values as the heads in two calls
+    torch.manual_seed(0)
+    pool = torch.randn(4, 1, 16, 16, device=DEV)
+    q = torch.randn(1, 40, 16, device=DEV)
+    out = torch.empty_like(q)
+    halves = [torch.empty(1, 20, 16, device=DEV) for _ in range(2)]
+    for heads, into in ((q, out), (q[:, :20].contiguous(), halves[0]), (q[:, 20:].contiguous(), halves[1])):
+        ops.paged_attention(heads, pool, pool, into, case["positions"], case["row_request"], case["table"],
                             scale=1.0, window=0, split_size=0, max_splits=1, scratch_acc=None, scratch_ml=None,
                             error_word=ops.new_error_word(DEV))
+    assert torch.equal(out, torch.cat(halves, dim=1))
 
 
 def test_sampling_kernel():
