@@ -7,10 +7,12 @@
 //
 // A block owns 16 query slots: `heads_per_block` heads of one row, or, when there are fewer than 16 heads, the
 // heads of several consecutive rows of one request (each row masked by its own position), and walks the keys
-// 64 at a time.  Its four warps share every step: for the scores each warp takes 16 of the 64 keys
-// (mma.sync m16n8k16, the row of queries against the key rows in shared memory); maxima and sums of the
-// softmax are exchanged through shared memory, in 32-bit; the weights go to shared memory as bfloat16 and
-// each warp multiplies them with its quarter of the value columns, which it keeps in registers (32-bit).
+// 64 at a time.  Its warps (eight when the value columns divide among them in whole 8-column tiles, else four)
+// share every step: for the scores each warp takes its share of the 64 keys (mma.sync m16n8k16, the row of
+// queries against the key rows in shared memory, two chains of accumulators so that consecutive products do not
+// wait for each other); maxima and sums of the softmax are exchanged through shared memory, in 32-bit; the weights
+// go to shared memory as bfloat16 and each warp multiplies them with its share of the value columns, which it keeps
+// in registers (32-bit).
 // Key tiles are aligned to absolute positions (multiples of 64), so a row's arithmetic depends on its own
 // position only, however the step was cut.  Two ways of launching:
 //   * tiles (prompt portions): int32 [n, 4] = (first row, rows <= 64, request, first position); a block takes
@@ -45,17 +47,20 @@ struct LaParams {
   float scale;
 };
 
-template <int NT_MAX>
-__global__ void __launch_bounds__(128)
+template <int NT_MAX, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 latent_attention_kernel(LaParams p) {
+  constexpr int THREADS = WARPS * 32;
+  constexpr int KEYS_PER_WARP = LA_KEYS / WARPS;          // 16 (two 8-key tiles) or 8 (one)
+  constexpr int ST = KEYS_PER_WARP / 8;
   extern __shared__ __align__(16) unsigned char la_smem[];
   const int d = p.d, vd = p.vd, pitch = d + LA_PAD;
   __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(la_smem);             // [64][pitch]
   __nv_bfloat16* q_tile = k_tile + LA_KEYS * pitch;                              // [16][pitch]
   __nv_bfloat16* p_tile = q_tile + LA_SLOTS * pitch;                             // [16][72]
-  float* warp_max = reinterpret_cast<float*>(p_tile + LA_SLOTS * (LA_KEYS + LA_PAD));   // [4][16]
-  float* warp_sum = warp_max + 4 * LA_SLOTS;                                     // [4][16]
-  long long* key_offset = reinterpret_cast<long long*>(warp_sum + 4 * LA_SLOTS); // [64]
+  float* warp_max = reinterpret_cast<float*>(p_tile + LA_SLOTS * (LA_KEYS + LA_PAD));   // [WARPS][16]
+  float* warp_sum = warp_max + WARPS * LA_SLOTS;                                 // [WARPS][16]
+  long long* key_offset = reinterpret_cast<long long*>(warp_sum + WARPS * LA_SLOTS);   // [64]
   srb_launch_dependents();
   srb_grid_dependency_wait();
 
@@ -85,7 +90,7 @@ latent_attention_kernel(LaParams p) {
 
   // the queries: slot m = (row m / hg of the block, head head0 + m % hg)
   const int chunks = d / 8;
-  for (int i = tid; i < LA_SLOTS * chunks; i += 128) {
+  for (int i = tid; i < LA_SLOTS * chunks; i += THREADS) {
     const int m = i / chunks, c = i - m * chunks;
     const int r = m / hg, head = head0 + m % hg;
     const bool valid = r < n_rows && head < p.n_q;
@@ -102,7 +107,7 @@ latent_attention_kernel(LaParams p) {
   const int limit_a = valid_a ? min(hi - 1, first_pos + r_a) : -1;      // the last key the slot sees
   const int limit_b = valid_b ? min(hi - 1, first_pos + r_b) : -1;
   float max_a = -INFINITY, max_b = -INFINITY, sum_a = 0.f, sum_b = 0.f;
-  const int cols_per_warp = vd / 4, nt = cols_per_warp / 8;
+  const int cols_per_warp = vd / WARPS, nt = cols_per_warp / 8;
   float acc[NT_MAX][4];
 #pragma unroll
   for (int j = 0; j < NT_MAX; ++j)
@@ -123,7 +128,7 @@ latent_attention_kernel(LaParams p) {
       key_offset[tid] = offset;
     }
     __syncthreads();
-    for (int i = tid; i < LA_KEYS * chunks; i += 128) {
+    for (int i = tid; i < LA_KEYS * chunks; i += THREADS) {
       const int key = i / chunks, c = i - key * chunks;
       const long long offset = key_offset[key];
       cp_async_16(k_tile + key * pitch + c * 8, offset < 0 ? p.pool : p.pool + offset + c * 8, offset < 0 ? 0 : 16);
@@ -132,23 +137,41 @@ latent_attention_kernel(LaParams p) {
     cp_async_wait<0>();
     __syncthreads();
 
-    // scores of this warp's 16 keys
-    float s[2][4] = {};
+    // scores of this warp's keys; even and odd steps along the row add into chains of their own
+    float s[ST][4] = {}, s_odd[ST][4] = {};
     const __nv_bfloat16* q_at = q_tile + (lane & 15) * pitch + (lane >> 4) * 8;
-    const __nv_bfloat16* k_at = k_tile + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * pitch + ((lane >> 3) & 1) * 8;
-    for (int kk = 0; kk < d; kk += 16) {
+    const __nv_bfloat16* k_at = ST == 2
+        ? k_tile + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * pitch + ((lane >> 3) & 1) * 8
+        : k_tile + (warp * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 8;
+    auto step = [&](int kk, float (&into)[ST][4]) {
       unsigned a[4], b0, b1, b2, b3;
       ldmatrix_x4(a[0], a[1], a[2], a[3], q_at + kk);
-      ldmatrix_x4(b0, b1, b2, b3, k_at + kk);
-      mma_bf16(s[0], a, b0, b1);
-      mma_bf16(s[1], a, b2, b3);
+      if (ST == 2) {
+        ldmatrix_x4(b0, b1, b2, b3, k_at + kk);
+        mma_bf16(into[0], a, b0, b1);
+        mma_bf16(into[ST - 1], a, b2, b3);
+      } else {
+        ldmatrix_x2(b0, b1, k_at + kk);
+        mma_bf16(into[0], a, b0, b1);
+      }
+    };
+    int kk = 0;
+#pragma unroll 2
+    for (; kk + 32 <= d; kk += 32) {
+      step(kk, s);
+      step(kk + 16, s_odd);
     }
+    if (kk < d) step(kk, s);
+#pragma unroll
+    for (int t = 0; t < ST; ++t)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[t][c] += s_odd[t][c];
     float tile_max_a = -INFINITY, tile_max_b = -INFINITY;
 #pragma unroll
-    for (int t = 0; t < 2; ++t)
+    for (int t = 0; t < ST; ++t)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const int key = base + warp * 16 + t * 8 + (lane & 3) * 2 + (c & 1);
+        const int key = base + warp * KEYS_PER_WARP + t * 8 + (lane & 3) * 2 + (c & 1);
         const bool seen = key >= lo && key <= ((c >> 1) ? limit_b : limit_a);
         s[t][c] = seen ? s[t][c] * p.scale : -INFINITY;
         if (c >> 1) tile_max_b = fmaxf(tile_max_b, s[t][c]); else tile_max_a = fmaxf(tile_max_a, s[t][c]);
@@ -164,7 +187,7 @@ latent_attention_kernel(LaParams p) {
     __syncthreads();
     float new_a = max_a, new_b = max_b;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       new_a = fmaxf(new_a, warp_max[w * LA_SLOTS + m_a]);
       new_b = fmaxf(new_b, warp_max[w * LA_SLOTS + m_b]);
     }
@@ -172,12 +195,12 @@ latent_attention_kernel(LaParams p) {
     const float corr_a = expf(max_a - safe_a), corr_b = expf(max_b - safe_b);     // exp(-inf) = 0 before the first key
     float part_a = 0.f, part_b = 0.f;
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
+    for (int t = 0; t < ST; ++t) {
       const float p0 = expf(s[t][0] - safe_a), p1 = expf(s[t][1] - safe_a);
       const float p2 = expf(s[t][2] - safe_b), p3 = expf(s[t][3] - safe_b);
       part_a += p0 + p1;
       part_b += p2 + p3;
-      const int col = warp * 16 + t * 8 + (lane & 3) * 2;
+      const int col = warp * KEYS_PER_WARP + t * 8 + (lane & 3) * 2;
       *reinterpret_cast<unsigned*>(p_tile + m_a * (LA_KEYS + LA_PAD) + col) = pack_bf16(p0, p1);
       *reinterpret_cast<unsigned*>(p_tile + m_b * (LA_KEYS + LA_PAD) + col) = pack_bf16(p2, p3);
     }
@@ -197,8 +220,14 @@ latent_attention_kernel(LaParams p) {
     max_a = new_a;
     max_b = new_b;
     __syncthreads();
-    sum_a = sum_a * corr_a + ((warp_sum[m_a] + warp_sum[LA_SLOTS + m_a]) + (warp_sum[2 * LA_SLOTS + m_a] + warp_sum[3 * LA_SLOTS + m_a]));
-    sum_b = sum_b * corr_b + ((warp_sum[m_b] + warp_sum[LA_SLOTS + m_b]) + (warp_sum[2 * LA_SLOTS + m_b] + warp_sum[3 * LA_SLOTS + m_b]));
+    float tile_sum_a = 0.f, tile_sum_b = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {                     // in warp order: the same sum in every thread
+      tile_sum_a += warp_sum[w * LA_SLOTS + m_a];
+      tile_sum_b += warp_sum[w * LA_SLOTS + m_b];
+    }
+    sum_a = sum_a * corr_a + tile_sum_a;
+    sum_b = sum_b * corr_b + tile_sum_b;
 
     // weights times this warp's value columns
     const __nv_bfloat16* p_at = p_tile + (lane & 15) * (LA_KEYS + LA_PAD) + (lane >> 4) * 8;
@@ -259,11 +288,11 @@ extern "C" int srb_latent_attention_supports(int d, int vd) {
   return d > 0 && d % 16 == 0 && vd > 0 && vd % 32 == 0 && vd <= 512 && vd <= d;
 }
 
-template <int NT_MAX>
+template <int NT_MAX, int WARPS>
 static int launch_latent_attention(const LaParams& p, dim3 grid, size_t smem, cudaStream_t s) {
   if (smem > 48 * 1024)
-    SRB_CUDA_CALL(cudaFuncSetAttribute(latent_attention_kernel<NT_MAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SRB_CUDA_CALL(srb_launch(latent_attention_kernel<NT_MAX>, grid, dim3(128), smem, s, p));
+    SRB_CUDA_CALL(cudaFuncSetAttribute(latent_attention_kernel<NT_MAX, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SRB_CUDA_CALL(srb_launch(latent_attention_kernel<NT_MAX, WARPS>, grid, dim3(WARPS * 32), smem, s, p));
   SRB_LAUNCH_CHECK("latent_attention");
   return SRB_OK;
 }
@@ -302,14 +331,16 @@ extern "C" int srb_latent_attention(const void* q, const void* pool, void* out, 
   }
   if (grid.y > 65535 || grid.z > 65535) SRB_FAIL("latent_attention: too many blocks for one launch");
   const size_t pitch = d + LA_PAD;
-  const size_t smem = (LA_KEYS + LA_SLOTS) * pitch * 2 + LA_SLOTS * (LA_KEYS + LA_PAD) * 2 + 8 * LA_SLOTS * 4 + LA_KEYS * 8;
+  const int warps = vd % 64 == 0 ? 8 : 4;                 // every warp gets whole 8-column tiles of the values
+  const size_t smem = (LA_KEYS + LA_SLOTS) * pitch * 2 + LA_SLOTS * (LA_KEYS + LA_PAD) * 2 + 2 * warps * LA_SLOTS * 4 + LA_KEYS * 8;
   if (smem > 227 * 1024) SRB_FAIL("latent_attention: %zu bytes of shared memory exceed 232448", smem);
   cudaStream_t s = (cudaStream_t)stream;
-  const int nt = vd / 32;
+  const int nt = vd / (8 * warps);
   int status;
-  if (nt <= 4) status = launch_latent_attention<4>(p, grid, smem, s);
-  else if (nt <= 8) status = launch_latent_attention<8>(p, grid, smem, s);
-  else status = launch_latent_attention<16>(p, grid, smem, s);
+  if (warps == 8) status = nt <= 4 ? launch_latent_attention<4, 8>(p, grid, smem, s) : launch_latent_attention<8, 8>(p, grid, smem, s);
+  else if (nt <= 4) status = launch_latent_attention<4, 4>(p, grid, smem, s);
+  else if (nt <= 8) status = launch_latent_attention<8, 4>(p, grid, smem, s);
+  else status = launch_latent_attention<16, 4>(p, grid, smem, s);
   if (status != SRB_OK || tiles) return status;
   AttnParams m = {};
   m.positions = positions; m.n_q = n_q; m.n_kv = 1; m.head_dim = d; m.window = 0; m.split_size = split_size;

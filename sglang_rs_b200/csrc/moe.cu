@@ -113,7 +113,7 @@ extern "C" int srb_moe_route(const void* h, const void* router, int rows, int wi
   if (top <= 0 || top > experts || top > 32) SRB_FAIL("moe_route: %d chosen experts are outside 1 .. min(%d, 32)", top, experts);
   if (width <= 0) SRB_FAIL("moe_route: width %d must be positive", width);
   cudaStream_t s = (cudaStream_t)stream;
-  const int block = experts >= 8 ? 256 : 32 * experts;
+  const int block = experts >= 32 ? 1024 : 32 * experts;          // a warp per expert, up to 32 warps
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(moe_route_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)h, (const float*)router,
                              width, experts, top, renormalize, chosen, weights));

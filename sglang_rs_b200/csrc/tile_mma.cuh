@@ -107,16 +107,18 @@ __device__ __forceinline__ int tile_mma_col(int j, int c) {
 
 // ---- the same product on a 128 x 64 tile with asynchronous copies ----------------------------------------------
 // For operands whose rows start on 16-byte boundaries (n_in a multiple of 8, aligned bases): 256 threads, warp (wy, wx)
-// of a 4 x 2 grid owns 32 rows x 32 columns as above; K is walked 32 at a time through a ring of three stages that
+// of a 4 x 2 grid owns 32 rows x 32 columns as above; K is walked 64 at a time through a ring of three stages that
 // cp.async fills two steps ahead, so a block keeps two steps of operands in flight while it multiplies a third.  A
 // tile of 128 rows reads each weight tile half as often as two tiles of 64 would.
 #define TA_ROWS 128
 #define TA_COLS 64
 #define TA_STAGES 3
+#define TA_K 64                    // a whole 128-byte line of every row per step
+#define TA_PITCH (TA_K + 8)
 
 template <int NW> struct TileAsyncSmem {
-  __nv_bfloat16 a[TA_STAGES][TA_ROWS][TM_PITCH];
-  __nv_bfloat16 w[TA_STAGES][NW][TA_COLS][TM_PITCH];
+  __nv_bfloat16 a[TA_STAGES][TA_ROWS][TA_PITCH];
+  __nv_bfloat16 w[TA_STAGES][NW][TA_COLS][TA_PITCH];
   const __nv_bfloat16* a_row[TA_ROWS];
 };
 
@@ -135,23 +137,25 @@ __device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, cons
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[m][i][j][c] = 0.f;
-  const int steps = (n_in + TM_K - 1) / TM_K;
+  const int steps = (n_in + TA_K - 1) / TA_K;
   auto issue = [&](int step) {
     if (step < steps) {
-      const int stage = step % TA_STAGES, k0 = step * TM_K;
+      const int stage = step % TA_STAGES, k0 = step * TA_K;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {                                       // 128 rows x 4 pieces of A
-        const int piece = tid + h * 256, row = piece >> 2, k = k0 + (piece & 3) * 8;
+      for (int h = 0; h < 4; ++h) {                                       // 128 rows x 8 pieces of A
+        const int piece = tid + h * 256, row = piece >> 3, k = k0 + (piece & 7) * 8;
         const __nv_bfloat16* a = s.a_row[row];
         const bool there = a != nullptr && k < n_in;
-        cp_async_16(&s.a[stage][row][(piece & 3) * 8], there ? a + k : w_base[0], there ? 16 : 0);
+        cp_async_16(&s.a[stage][row][(piece & 7) * 8], there ? a + k : w_base[0], there ? 16 : 0);
       }
 #pragma unroll
-      for (int m = 0; m < NW; ++m) {                                      // 64 rows x 4 pieces of each W
-        const int row = tid >> 2, k = k0 + (tid & 3) * 8;
-        const bool there = row < cols_valid && k < n_in;
-        cp_async_16(&s.w[stage][m][row][(tid & 3) * 8], there ? w_base[m] + (size_t)row * n_in + k : w_base[0], there ? 16 : 0);
-      }
+      for (int m = 0; m < NW; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                                     // 64 rows x 8 pieces of each W
+          const int piece = tid + h * 256, row = piece >> 3, k = k0 + (piece & 7) * 8;
+          const bool there = row < cols_valid && k < n_in;
+          cp_async_16(&s.w[stage][m][row][(piece & 7) * 8], there ? w_base[m] + (size_t)row * n_in + k : w_base[0], there ? 16 : 0);
+        }
     }
     cp_async_commit();                                                    // an empty group keeps the count in step
   };
@@ -165,7 +169,7 @@ __device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, cons
     if (wy * 32 >= rows_valid) continue;                                  // (the same for all lanes of the warp)
     const bool second = wy * 32 + 16 < rows_valid;
 #pragma unroll
-    for (int kk = 0; kk < TM_K; kk += 16) {
+    for (int kk = 0; kk < TA_K; kk += 16) {
       unsigned a[2][4];
       ldmatrix_x4(a[0][0], a[0][1], a[0][2], a[0][3], &s.a[stage][wy * 32 + (lane & 15)][kk + (lane >> 4) * 8]);
       if (second) ldmatrix_x4(a[1][0], a[1][1], a[1][2], a[1][3], &s.a[stage][wy * 32 + 16 + (lane & 15)][kk + (lane >> 4) * 8]);

@@ -165,7 +165,7 @@ def test_attention_over_shared_rows_with_a_sink(dtype, heads, split):
     assert int(word.item()) == 0
 
 
-@pytest.mark.parametrize("heads,width,value_dim", [(3, 48, 32), (8, 80, 64), (16, 144, 96), (34, 32, 32)])
+@pytest.mark.parametrize("heads,width,value_dim", [(3, 48, 32), (8, 80, 64), (16, 144, 96), (34, 32, 32), (5, 160, 128), (2, 528, 512)])
 def test_tensor_core_attention_over_shared_rows(heads, width, value_dim):
     """The bfloat16 kernel for rows that are key and value: prompt portions given as tiles (several requests, a portion
     that starts in the middle of a page and of a 64-key block, rows outside the tiles untouched) and decoded rows whose
