@@ -138,24 +138,41 @@ __device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[m][i][j][c] = 0.f;
   const int steps = (n_in + TA_K - 1) / TA_K;
+  // What a thread copies per step is fixed but for the step's offset along K: four 16-byte pieces of A (128 rows x 8
+  // pieces) and two of each W (64 rows x 8 pieces).  Rows of A that do not exist are not copied at all: a row's result
+  // depends on its own row only, and the results of such rows are never stored.
+  const __nv_bfloat16* a_src[4];
+  const __nv_bfloat16* w_src[NW][2];
+  int a_at[4], w_at[2], k_of[4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const int piece = tid + h * 256, row = piece >> 3;
+    k_of[h] = (piece & 7) * 8;
+    a_at[h] = row * TA_PITCH + k_of[h];
+    const __nv_bfloat16* a = row < rows_valid ? s.a_row[row] : nullptr;
+    a_src[h] = a ? a + k_of[h] : nullptr;
+    if (h < 2) {
+      w_at[h] = row * TA_PITCH + k_of[h];
+#pragma unroll
+      for (int m = 0; m < NW; ++m) w_src[m][h] = row < cols_valid ? w_base[m] + (size_t)row * n_in + k_of[h] : nullptr;
+    }
+  }
   auto issue = [&](int step) {
     if (step < steps) {
       const int stage = step % TA_STAGES, k0 = step * TA_K;
+      __nv_bfloat16* a_stage = &s.a[stage][0][0];
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {                                       // 128 rows x 8 pieces of A
-        const int piece = tid + h * 256, row = piece >> 3, k = k0 + (piece & 7) * 8;
-        const __nv_bfloat16* a = s.a_row[row];
-        const bool there = a != nullptr && k < n_in;
-        cp_async_16(&s.a[stage][row][(piece & 7) * 8], there ? a + k : w_base[0], there ? 16 : 0);
-      }
+      for (int h = 0; h < 4; ++h)
+        if (a_src[h]) cp_async_16(a_stage + a_at[h], a_src[h] + k0, k0 + k_of[h] < n_in ? 16 : 0);
 #pragma unroll
-      for (int m = 0; m < NW; ++m)
+      for (int m = 0; m < NW; ++m) {
+        __nv_bfloat16* w_stage = &s.w[stage][m][0][0];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {                                     // 64 rows x 8 pieces of each W
-          const int piece = tid + h * 256, row = piece >> 3, k = k0 + (piece & 7) * 8;
-          const bool there = row < cols_valid && k < n_in;
-          cp_async_16(&s.w[stage][m][row][(piece & 7) * 8], there ? w_base[m] + (size_t)row * n_in + k : w_base[0], there ? 16 : 0);
+        for (int h = 0; h < 2; ++h) {
+          const bool there = w_src[m][h] != nullptr && k0 + k_of[h] < n_in;
+          cp_async_16(w_stage + w_at[h], there ? w_src[m][h] + k0 : w_base[0], there ? 16 : 0);
         }
+      }
     }
     cp_async_commit();                                                    // an empty group keeps the count in step
   };
