@@ -12,8 +12,9 @@
 // cuda_attention.rs:137-151.
 //
 // Two terms that other designs add, both off by default:
-//  * a sink: with `sinks` (one float per query head) the denominator also holds exp(sink_h), a term
-//    without key or value that is not scaled and counts once per row, however the keys are split;
+//  * a sink: `sinks` holds one float per query head; exp(sink_h) is added to the softmax's denominator and to nothing
+//    else.  It belongs to no key, gets no share of the values, is taken as it is (the score scale does not apply), and is
+//    added exactly one time per row, also when the row's keys are split over several blocks (the merge adds it);
 //  * values narrower than keys: the output and the value rows are `value_dim` wide.  With
 //    `shared_values` the value of a key is the first `value_dim` entries of its key row (a cache that
 //    keeps one latent row per token serves as key and as value), and v_pool is not read.

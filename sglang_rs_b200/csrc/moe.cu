@@ -23,6 +23,14 @@ SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
 
 #define MOE_ROWS 128     // rows of a tile of the plan: slots of one expert that one block (or two) takes
+#define MOE_FEW_ROWS 32  // ... when the step's choices are few per expert (decoded tokens): tiles are then almost empty,
+                         // and the products' blocks trade the rows of the A buffer for stages of weights in flight
+#define MOE_FEW_STAGES 4
+
+// The tile size is a function of the step's shape only, so every launch of a step agrees on it.
+static inline int moe_tile_rows(int rows, int top, int experts) {
+  return (long long)rows * top <= 8LL * experts ? MOE_FEW_ROWS : MOE_ROWS;
+}
 #define MOE_TILE 64      // rows that the smaller kernels take at a time (half a tile), and output columns of a block
 #define MOE_K 16
 #define MOE_MAX_EXPERTS 1024
@@ -129,7 +137,7 @@ extern "C" int srb_moe_route(const void* h, const void* router, int rows, int wi
 // One block.  plan: [0] number of tiles, then offsets[experts + 1], then per tile (expert, first slot).
 // slot_row[slot]: the row whose entry sits in the slot; entry_slot[row * top + k]: the slot of that entry.
 __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int top, int experts, int max_tiles,
-                                int* __restrict__ plan, int* __restrict__ slot_row, int* __restrict__ entry_slot,
+                                int tile_rows, int* __restrict__ plan, int* __restrict__ slot_row, int* __restrict__ entry_slot,
                                 int* error_word) {
   __shared__ int count[MOE_MAX_EXPERTS];
   __shared__ int first[MOE_MAX_EXPERTS + 1];
@@ -149,7 +157,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
       first[e] = slots;
       tile_first[e] = tiles;
       slots += count[e];
-      tiles += (count[e] + MOE_ROWS - 1) / MOE_ROWS;
+      tiles += (count[e] + tile_rows - 1) / tile_rows;
     }
     first[experts] = slots;
     tile_first[experts] = tiles;
@@ -166,7 +174,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
       const int at = tile_first[e] + t;
       if (at < max_tiles) {
         tiles[2 * at] = e;
-        tiles[2 * at + 1] = first[e] + t * MOE_ROWS;
+        tiles[2 * at + 1] = first[e] + t * tile_rows;
       }
     }
     count[e] = 0;                       // becomes the number of the expert's slots handed out so far
@@ -182,18 +190,21 @@ __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int
 }
 
 extern "C" int srb_moe_plan_ints(int rows, int top, int experts) {
-  const int max_tiles = (rows * top) / MOE_ROWS + experts;
+  const int max_tiles = (rows * top) / moe_tile_rows(rows, top, experts) + experts;
   return 1 + experts + 1 + 2 * max_tiles;
 }
 
-extern "C" int srb_moe_max_tiles(int rows, int top, int experts) { return (rows * top) / MOE_ROWS + experts; }
+extern "C" int srb_moe_max_tiles(int rows, int top, int experts) {
+  return (rows * top) / moe_tile_rows(rows, top, experts) + experts;
+}
 
 extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, int* plan, int* slot_row, int* entry_slot,
                             int* error_word, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0) SRB_FAIL("moe_plan: %d experts, %d chosen", experts, top);
   SRB_CUDA_CALL(srb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, chosen, rows * top, top, experts,
-                           srb_moe_max_tiles(rows, top, experts), plan, slot_row, entry_slot, error_word));
+                           srb_moe_max_tiles(rows, top, experts), moe_tile_rows(rows, top, experts), plan, slot_row,
+                           entry_slot, error_word));
   SRB_LAUNCH_CHECK("moe_plan");
   return SRB_OK;
 }
@@ -205,7 +216,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b,
                    const int* __restrict__ plan, const int* __restrict__ slot_row, int experts, int n_in, int n_out,
-                   int activation, T* __restrict__ out_t, float* __restrict__ out_f) {
+                   int activation, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows) {
   __shared__ float x_tile[MOE_K][MOE_TILE + 4];
   __shared__ float a_tile[MOE_K][MOE_TILE + 4];
   __shared__ float b_tile[GATED ? MOE_K : 1][MOE_TILE + 4];
@@ -217,7 +228,7 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
   const int* offsets = plan + 1;
   const int* tiles = plan + 1 + experts + 1;
   const int expert = tiles[2 * tile], first = tiles[2 * tile + 1] + MOE_TILE * blockIdx.z;
-  const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  const int count = min(min(MOE_TILE, tile_rows - MOE_TILE * (int)blockIdx.z), offsets[expert + 1] - first);
   if (count <= 0) return;
   const int t = threadIdx.x;
   if (t < MOE_TILE) tile_row[t] = t < count ? (GATED ? slot_row[first + t] : first + t) : -1;
@@ -281,7 +292,7 @@ __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                        const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
                        const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
-                       __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f) {
+                       __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, int tile_rows) {
   __shared__ __align__(16) TileMmaSmem s;
   srb_launch_dependents();
   srb_grid_dependency_wait();
@@ -290,7 +301,7 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   const int* offsets = plan + 1;
   const int* tiles = plan + 1 + experts + 1;
   const int expert = tiles[2 * tile], first = tiles[2 * tile + 1] + MOE_TILE * blockIdx.z;
-  const int count = min(MOE_TILE, offsets[expert + 1] - first);
+  const int count = min(min(MOE_TILE, tile_rows - MOE_TILE * (int)blockIdx.z), offsets[expert + 1] - first);
   if (count <= 0) return;
   const int t = threadIdx.x;
   if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
@@ -324,7 +335,7 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 
 // A whole tile (up to 128 slots) times 64 output columns, operands through a ring of asynchronous copies
 // (tile_mma.cuh); for rows that start on 16-byte boundaries.
-template <bool GATED>
+template <bool GATED, int ROWS, int STAGES>
 __global__ void __launch_bounds__(256)
 moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                          const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
@@ -332,7 +343,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                          __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f) {
   constexpr int NW = GATED ? 2 : 1;
   extern __shared__ __align__(16) unsigned char moe_smem[];
-  TileAsyncSmem<NW>& s = *reinterpret_cast<TileAsyncSmem<NW>*>(moe_smem);
+  TileAsyncSmem<NW, ROWS, STAGES>& s = *reinterpret_cast<TileAsyncSmem<NW, ROWS, STAGES>*>(moe_smem);
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int tile = blockIdx.y;
@@ -340,19 +351,19 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   const int* offsets = plan + 1;
   const int* tiles = plan + 1 + experts + 1;
   const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
-  const int count = min(MOE_ROWS, offsets[expert + 1] - first);
+  const int count = min(ROWS, offsets[expert + 1] - first);
   const int t = threadIdx.x;
-  if (t < MOE_ROWS) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
+  if (t < ROWS) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
   const int col0 = blockIdx.x * TA_COLS;
   const size_t matrix = (size_t)expert * n_out * n_in + (size_t)col0 * n_in;
   float acc[NW][2][4][4];
   if (GATED) {
     const __nv_bfloat16* const bases[2] = {w_a + matrix, w_b + matrix};
-    tile_mma_128x64_async<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
+    tile_mma_128x64_async<NW, ROWS, STAGES>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
   } else {
     const __nv_bfloat16* const bases[2] = {w_a + matrix, nullptr};
-    tile_mma_128x64_async<NW>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
+    tile_mma_128x64_async<NW, ROWS, STAGES>(s, reinterpret_cast<const __nv_bfloat16* const(&)[NW]>(bases), n_out - col0, count, n_in, acc);
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
@@ -386,23 +397,27 @@ template <typename T>
 static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
                                const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
                                void* out_t, float* out_f, cudaStream_t s) {
-  dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts), MOE_ROWS / MOE_TILE);
+  const int tile_rows = moe_tile_rows(rows, top, experts);
+  dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts), (tile_rows + MOE_TILE - 1) / MOE_TILE);
   if (grid.y > 65535) SRB_FAIL("moe product: %d tiles exceed one launch", (int)grid.y);
   if (sizeof(T) == 2 && n_in % 8 == 0 && (((uintptr_t)x | (uintptr_t)w_a | (uintptr_t)w_b) & 15) == 0) {
     // bfloat16 rows on 16-byte boundaries: whole tiles, operands by asynchronous copies
     grid.z = 1;
-    const size_t smem = gated ? sizeof(TileAsyncSmem<2>) : sizeof(TileAsyncSmem<1>);
-    if (gated) {
-      SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<true>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x,
-                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f));
+#define MOE_ASYNC_LAUNCH(GATED, ROWS, STAGES)                                                                          \
+  do {                                                                                                                 \
+    const size_t smem = sizeof(TileAsyncSmem<(GATED) ? 2 : 1, ROWS, STAGES>);                                          \
+    SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<GATED, ROWS, STAGES>,                                  \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                       \
+    SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<GATED, ROWS, STAGES>, grid, dim3(256), smem, s,                  \
+                             (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan,      \
+                             slot_row, experts, n_in, n_out, activation, (__nv_bfloat16*)out_t, out_f));               \
+  } while (0)
+    if (tile_rows == MOE_FEW_ROWS) {
+      if (gated) MOE_ASYNC_LAUNCH(true, MOE_FEW_ROWS, MOE_FEW_STAGES); else MOE_ASYNC_LAUNCH(false, MOE_FEW_ROWS, MOE_FEW_STAGES);
     } else {
-      SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<false>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x,
-                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f));
+      if (gated) MOE_ASYNC_LAUNCH(true, MOE_ROWS, TA_STAGES); else MOE_ASYNC_LAUNCH(false, MOE_ROWS, TA_STAGES);
     }
+#undef MOE_ASYNC_LAUNCH
     SRB_LAUNCH_CHECK("moe product");
     return SRB_OK;
   }
@@ -411,20 +426,20 @@ static int launch_moe_products(bool gated, const void* x, const void* w_a, const
     if (gated)
       SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                                (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f));
+                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows));
     else
       SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                                (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f));
+                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows));
     SRB_LAUNCH_CHECK("moe product");
     return SRB_OK;
   }
   if (gated)
     SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, true>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f));
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows));
   else
     SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, false>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f));
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows));
   SRB_LAUNCH_CHECK("moe product");
   return SRB_OK;
 }

@@ -116,17 +116,20 @@ __device__ __forceinline__ int tile_mma_col(int j, int c) {
 #define TA_K 64                    // a whole 128-byte line of every row per step
 #define TA_PITCH (TA_K + 8)
 
-template <int NW> struct TileAsyncSmem {
-  __nv_bfloat16 a[TA_STAGES][TA_ROWS][TA_PITCH];
-  __nv_bfloat16 w[TA_STAGES][NW][TA_COLS][TA_PITCH];
-  const __nv_bfloat16* a_row[TA_ROWS];
+// ROWS: rows of the A tile (128, or 32 for tiles that hold a few decoded tokens: the room that the smaller A buffer
+// leaves goes into more stages, since such a tile has nothing to multiply and only streams its weights).
+template <int NW, int ROWS = TA_ROWS, int STAGES = TA_STAGES> struct TileAsyncSmem {
+  __nv_bfloat16 a[STAGES][ROWS][TA_PITCH];
+  __nv_bfloat16 w[STAGES][NW][TA_COLS][TA_PITCH];
+  const __nv_bfloat16* a_row[ROWS];
 };
 
 // rows_valid: rows of the tile that exist; a warp whose 16-row groups lie behind them multiplies nothing (with a few
 // decoded tokens per expert most of the tile is empty, and the products of empty rows would cost more than the copies).
-template <int NW>
-__device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, const __nv_bfloat16* const (&w_base)[NW],
+template <int NW, int ROWS = TA_ROWS, int STAGES = TA_STAGES>
+__device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW, ROWS, STAGES>& s, const __nv_bfloat16* const (&w_base)[NW],
                                                       int cols_valid, int rows_valid, int n_in, float (&acc)[NW][2][4][4]) {
+  constexpr int A_PIECES = ROWS * 8 / 256;                 // 16-byte pieces of A that a thread copies per step
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wy = warp >> 1, wx = warp & 1;
 #pragma unroll
@@ -141,35 +144,38 @@ __device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, cons
   // What a thread copies per step is fixed but for the step's offset along K: four 16-byte pieces of A (128 rows x 8
   // pieces) and two of each W (64 rows x 8 pieces).  Rows of A that do not exist are not copied at all: a row's result
   // depends on its own row only, and the results of such rows are never stored.
-  const __nv_bfloat16* a_src[4];
+  const __nv_bfloat16* a_src[A_PIECES];
   const __nv_bfloat16* w_src[NW][2];
-  int a_at[4], w_at[2], k_of[4];
+  int a_at[A_PIECES], w_at[2];
+  const int k_of = (tid & 7) * 8;                          // the same for every piece of a thread (256 is a multiple of 8)
 #pragma unroll
-  for (int h = 0; h < 4; ++h) {
-    const int piece = tid + h * 256, row = piece >> 3;
-    k_of[h] = (piece & 7) * 8;
-    a_at[h] = row * TA_PITCH + k_of[h];
+  for (int h = 0; h < A_PIECES; ++h) {
+    const int row = (tid + h * 256) >> 3;
+    a_at[h] = row * TA_PITCH + k_of;
     const __nv_bfloat16* a = row < rows_valid ? s.a_row[row] : nullptr;
-    a_src[h] = a ? a + k_of[h] : nullptr;
-    if (h < 2) {
-      w_at[h] = row * TA_PITCH + k_of[h];
+    a_src[h] = a ? a + k_of : nullptr;
+  }
 #pragma unroll
-      for (int m = 0; m < NW; ++m) w_src[m][h] = row < cols_valid ? w_base[m] + (size_t)row * n_in + k_of[h] : nullptr;
-    }
+  for (int h = 0; h < 2; ++h) {
+    const int row = (tid + h * 256) >> 3;
+    w_at[h] = row * TA_PITCH + k_of;
+#pragma unroll
+    for (int m = 0; m < NW; ++m) w_src[m][h] = row < cols_valid ? w_base[m] + (size_t)row * n_in + k_of : nullptr;
   }
   auto issue = [&](int step) {
     if (step < steps) {
-      const int stage = step % TA_STAGES, k0 = step * TA_K;
+      const int stage = step % STAGES, k0 = step * TA_K;
+      const bool inside = k0 + k_of < n_in;
       __nv_bfloat16* a_stage = &s.a[stage][0][0];
 #pragma unroll
-      for (int h = 0; h < 4; ++h)
-        if (a_src[h]) cp_async_16(a_stage + a_at[h], a_src[h] + k0, k0 + k_of[h] < n_in ? 16 : 0);
+      for (int h = 0; h < A_PIECES; ++h)
+        if (a_src[h]) cp_async_16(a_stage + a_at[h], a_src[h] + k0, inside ? 16 : 0);
 #pragma unroll
       for (int m = 0; m < NW; ++m) {
         __nv_bfloat16* w_stage = &s.w[stage][m][0][0];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const bool there = w_src[m][h] != nullptr && k0 + k_of[h] < n_in;
+          const bool there = w_src[m][h] != nullptr && inside;
           cp_async_16(w_stage + w_at[h], there ? w_src[m][h] + k0 : w_base[0], there ? 16 : 0);
         }
       }
@@ -177,13 +183,13 @@ __device__ __forceinline__ void tile_mma_128x64_async(TileAsyncSmem<NW>& s, cons
     cp_async_commit();                                                    // an empty group keeps the count in step
   };
 #pragma unroll
-  for (int step = 0; step < TA_STAGES - 1; ++step) issue(step);
+  for (int step = 0; step < STAGES - 1; ++step) issue(step);
   for (int step = 0; step < steps; ++step) {
-    cp_async_wait<TA_STAGES - 2>();                                       // the copies of this step have landed
+    cp_async_wait<STAGES - 2>();                                       // the copies of this step have landed
     __syncthreads();                                                      // ... for every thread, and the step before is multiplied
-    issue(step + TA_STAGES - 1);                                          // into the stage that was multiplied last
-    const int stage = step % TA_STAGES;
-    if (wy * 32 >= rows_valid) continue;                                  // (the same for all lanes of the warp)
+    issue(step + STAGES - 1);                                             // into the stage that was multiplied last
+    const int stage = step % STAGES;
+    if (wy * 32 >= rows_valid || wy * 32 >= ROWS) continue;                                  // (the same for all lanes of the warp)
     const bool second = wy * 32 + 16 < rows_valid;
 #pragma unroll
     for (int kk = 0; kk < TA_K; kk += 16) {

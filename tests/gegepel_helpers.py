@@ -64,6 +64,14 @@ SMALL_D = config(64, 90, [
 ], loop=(1, 3, 2), scale=1.3)
 
 
+#: no size is a multiple of eight: rows that start off 16-byte borders, tiles with ragged ends in every kernel
+SMALL_E = config(36, 50, [
+    layer(mixer(3, 10, 6, 14, 12, 20), moe(3, 2, 20)),
+    layer(mixer(2, 6, 4, 10, 20, 12, rot_dims=2), None),
+    layer(mixer(1, 12, 2, 6, 10, 18), moe(5, 4, 12)),
+], loop=(0, 1, 2), scale=0.8)
+
+
 def make_folder(tmp_path, name: str, doc: dict, seed: int, dtype: torch.dtype, sharpen: float = 3.0) -> str:
     """A model folder from the engine's random-weights mode, changed so that faults show: the query latent's
     scale is multiplied by ``sharpen`` (peaked attention), sinks are spread (a sink that is left out or counted

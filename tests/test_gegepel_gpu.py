@@ -260,7 +260,7 @@ def test_routed_experts(dtype, experts, top, rows):
 
 # ------------------------------------------------------------------------------ whole models, every way of cutting
 @pytest.mark.parametrize("dtype_name,stored,tolerance", DTYPES)
-@pytest.mark.parametrize("doc", [gh.SMALL_A, gh.SMALL_B, gh.SMALL_C, gh.SMALL_D], ids=["a", "b", "c", "d"])
+@pytest.mark.parametrize("doc", [gh.SMALL_A, gh.SMALL_B, gh.SMALL_C, gh.SMALL_D, gh.SMALL_E], ids=["a", "b", "c", "d", "e"])
 def test_prompts_tails_portions_and_mixed_batches(tmp_path, doc, dtype_name, stored, tolerance):
     folder = gh.make_folder(tmp_path, "m", doc, seed=5, dtype=stored)
     requests = gh.random_requests(doc, (1, 2, 23, 64, 65, 150, 131), seed=3)
