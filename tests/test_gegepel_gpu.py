@@ -163,6 +163,16 @@ def test_attention_over_shared_rows_with_a_sink(dtype, heads, split):
         if r == 0:
             assert float(w[0, 3]) > 0.5
     assert int(word.item()) == 0
+    # values in a pool of their own, narrower than the keys, without a sink
+    values = torch.randn(length, value_dim)
+    v_pool = torch.zeros((12, 1, page, value_dim), dtype=dtype, device=DEV)
+    for p in range(length):
+        v_pool[pages[p // page], 0, p % page] = values[p].to(dtype)
+    ops.paged_attention(q.to(DEV, dtype), pool, v_pool, out, positions.to(DEV), torch.zeros(2, dtype=torch.int32, device=DEV), table,
+                        scale=0.3, window=0, split_size=split, max_splits=splits, scratch_acc=acc, scratch_ml=ml, error_word=word)
+    for r, pos in enumerate(positions.tolist()):
+        scores = torch.einsum("hd,jd->hj", seen(q, dtype)[r], k[:pos + 1]) * 0.3
+        close(out[r], torch.softmax(scores, -1) @ seen(values, dtype)[:pos + 1], dtype, f"row {r}, own values")
 
 
 @pytest.mark.parametrize("heads,width,value_dim", [(3, 48, 32), (8, 80, 64), (16, 144, 96), (34, 32, 32), (5, 160, 128), (2, 528, 512)])
