@@ -60,6 +60,11 @@ struct GemmArgs {
   int activation;            // EPI_SILU: which SRB_ACT_* is applied to the gate half
   int k_blocks_per_split;
   int* error_word;
+  // Grouped products (routed experts): `plan` (device) = [number of tiles, first slot of every expert (experts + 1),
+  // then (expert, first slot) per tile]; blockIdx.x names a tile, whose tokens are the slots first .. first +
+  // BLOCK_T - 1 as far as they belong to the expert, and whose weight rows start at expert * expert_rows.  Null: off.
+  const int* plan;
+  int experts, expert_rows;
 };
 
 template <int BLOCK_T, int EPI, int STAGES>
@@ -82,7 +87,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // token tiles are the fastest grid dimension: blocks that share a weight tile run together
-  const int token0 = blockIdx.x * BLOCK_T;
+  int token0 = blockIdx.x * BLOCK_T, token_limit = args.tokens, w_row0 = 0;
+  if (args.plan) {
+    srb_grid_dependency_wait();                        // the plan is written by a kernel ahead
+    if ((int)blockIdx.x >= args.plan[0]) return;       // before any barrier or tensor memory exists
+    const int* first_slot = args.plan + 1;
+    const int* tiles = first_slot + args.experts + 1;
+    const int expert = tiles[2 * blockIdx.x];
+    token0 = tiles[2 * blockIdx.x + 1];
+    token_limit = min(token0 + BLOCK_T, first_slot[expert + 1]);
+    w_row0 = expert * args.expert_rows;
+  }
   const int feature0 = blockIdx.y * FEATURES_PER_BLOCK;
   const int total_k_blocks = (args.k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
   const int kb_begin = blockIdx.z * args.k_blocks_per_split;
@@ -123,8 +138,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int kx = (kb_begin + i) * GEMM_BLOCK_K;
       if (elect_one()) {
         mbar_expect_tx(bar, STAGE_BYTES);
-        tma_load_2d(stage, &map_w, bar, kx, feature0);
-        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, args.up_row_offset + feature0);
+        tma_load_2d(stage, &map_w, bar, kx, w_row0 + feature0);
+        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, w_row0 + args.up_row_offset + feature0);
       }
       issued = i + 1;
     }
@@ -144,8 +159,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int kx = (kb_begin + i) * GEMM_BLOCK_K;
       if (elect_one()) {
         mbar_expect_tx(bar, STAGE_BYTES);
-        tma_load_2d(stage, &map_w, bar, kx, feature0);
-        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, args.up_row_offset + feature0);
+        tma_load_2d(stage, &map_w, bar, kx, w_row0 + feature0);
+        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, w_row0 + args.up_row_offset + feature0);
         tma_load_2d(stage + A_BYTES, &map_x, bar, kx, token0);
       }
       issued = i + 1;
@@ -199,7 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const unsigned lane_address = tmem_base + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
     for (int c = 0; c < BLOCK_T; c += 16) {
-      if (token0 + c >= args.tokens) break;            // the same for all epilogue warps
+      if (token0 + c >= token_limit) break;            // the same for all epilogue warps
       float acc[16];
       if (ok && num_kb > 0) {
         tmem_load_16(lane_address + c, acc);
@@ -217,7 +232,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int token = token0 + c + j;
-            if (token >= args.tokens) break;
+            if (token >= token_limit) break;
             const float g = acc[j], u = exchange[((quarter & 1) * 32 + lane) * 16 + j];
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
                 __float2bfloat16_rn(srb_gated<true>(args.activation, g, u));
@@ -232,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int token = token0 + c + j;
-          if (token >= args.tokens) break;
+          if (token >= token_limit) break;
           if (EPI == EPI_BF16) {
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] = __float2bfloat16_rn(acc[j]);
           } else if (EPI == EPI_F32) {
@@ -388,6 +403,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
   GemmArgs args;
   args.out = out; args.tokens = tokens; args.features = features; args.k = k; args.ldo = ldo;
   args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
+  args.plan = nullptr; args.experts = 0; args.expert_rows = 0;
   args.k_blocks_per_split = (total_k_blocks + splits - 1) / splits;
   const int used_splits = (total_k_blocks + args.k_blocks_per_split - 1) / args.k_blocks_per_split;
   if (used_splits != splits) SRB_FAIL("gemm_bf16: %d splits leave one without work for %d blocks of K", splits, total_k_blocks);
@@ -399,4 +415,54 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
     case EPI_ADD: return dispatch_tokens<EPI_ADD>(block_t, map_w, map_x, args, splits, s);
     default: return dispatch_tokens<EPI_PARTIAL>(block_t, map_w, map_x, args, splits, s);
   }
+}
+
+
+// ---- grouped: one weight matrix per expert, tokens grouped by expert ------------------------------------------
+// x [slots, k]: the rows in slot order (the slots of an expert are consecutive); w [experts * expert_rows, k];
+// plan as in GemmArgs, with tiles of 128 slots and room for `max_tiles` of them.  mode 1: out float [slots, ldo] =
+// x w_e^T over `features` rows of the expert's matrix; mode 2: the expert's matrix stacks gate rows [0, features) over
+// up rows [up_row_offset, + features), out bf16 [slots, ldo] = act(gate) * up.  Blocks of tiles beyond the plan's
+// count leave at once; rows of a tile behind its expert's last slot are computed and not stored.
+template <int EPI>
+static int launch_grouped(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int max_tiles,
+                          cudaStream_t s) {
+  constexpr int BLOCK_T = 128;
+  constexpr int STAGE_BYTES = GEMM_BLOCK_F * GEMM_BLOCK_K * 2 + BLOCK_T * GEMM_BLOCK_K * 2;
+  constexpr int STAGES = 200 * 1024 / STAGE_BYTES;
+  constexpr int FEATURES_PER_BLOCK = EPI == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  auto kernel = gemm_bf16_kernel<BLOCK_T, EPI, STAGES>;
+  SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // tiles are the fastest grid dimension: the blocks of one feature block of one expert's neighbours run together
+  dim3 grid(max_tiles, (args.features + FEATURES_PER_BLOCK - 1) / FEATURES_PER_BLOCK, 1);
+  if (grid.y > 65535) SRB_FAIL("gemm_bf16_grouped: %d features exceed one launch", args.features);
+  SRB_CUDA_CALL(srb_launch(kernel, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args));
+  return SRB_OK;
+}
+
+extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, const int* plan, int max_tiles, int slots,
+                                     int experts, int expert_rows, int features, int k, int ldo, int up_row_offset,
+                                     int mode, int activation, int* error_word, void* stream) {
+  if (slots <= 0 || features <= 0 || max_tiles <= 0) return SRB_OK;
+  if (k <= 0 || k % 8 != 0) SRB_FAIL("gemm_bf16_grouped: inner size %d must be a positive multiple of 8", k);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16_grouped: operands must be 16-byte aligned");
+  if (mode != EPI_F32 && mode != EPI_SILU) SRB_FAIL("gemm_bf16_grouped: mode %d is not float or gated", mode);
+  if (mode == EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT)) SRB_FAIL("gemm_bf16_grouped: unknown activation %d", activation);
+  if (!plan || experts <= 0 || expert_rows <= 0) SRB_FAIL("gemm_bf16_grouped: a plan and the experts' sizes are needed");
+  if ((mode == EPI_SILU ? up_row_offset + features : features) > expert_rows)
+    SRB_FAIL("gemm_bf16_grouped: %d features do not fit the %d rows of an expert", features, expert_rows);
+  if (ldo < features) SRB_FAIL("gemm_bf16_grouped: output pitch %d is smaller than %d features", ldo, features);
+  CUtensorMap map_w, map_x;
+  if (make_map(&map_w, w, (long long)experts * expert_rows, k, k, mode == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F) != SRB_OK)
+    return SRB_ERR_INVALID;
+  if (make_map(&map_x, x, slots, k, k, 128) != SRB_OK) return SRB_ERR_INVALID;
+  GemmArgs args;
+  args.out = out; args.tokens = slots; args.features = features; args.k = k; args.ldo = ldo;
+  args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
+  args.plan = plan; args.experts = experts; args.expert_rows = expert_rows;
+  args.k_blocks_per_split = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
+  cudaStream_t s = (cudaStream_t)stream;
+  return mode == EPI_SILU ? launch_grouped<EPI_SILU>(map_w, map_x, args, max_tiles, s)
+                          : launch_grouped<EPI_F32>(map_w, map_x, args, max_tiles, s);
 }

@@ -216,7 +216,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b,
                    const int* __restrict__ plan, const int* __restrict__ slot_row, int experts, int n_in, int n_out,
-                   int activation, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows) {
+                   int activation, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
   __shared__ float x_tile[MOE_K][MOE_TILE + 4];
   __shared__ float a_tile[MOE_K][MOE_TILE + 4];
   __shared__ float b_tile[GATED ? MOE_K : 1][MOE_TILE + 4];
@@ -235,8 +235,8 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
   __syncthreads();
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int col0 = blockIdx.x * MOE_TILE;
-  const T* wa = w_a + (size_t)expert * n_out * n_in;
-  const T* wb = GATED ? w_b + (size_t)expert * n_out * n_in : nullptr;
+  const T* wa = w_a + (size_t)expert * expert_stride;
+  const T* wb = GATED ? w_b + (size_t)expert * expert_stride : nullptr;
   float acc_a[4][4] = {}, acc_b[GATED ? 4 : 1][4] = {};
   for (int k0 = 0; k0 < n_in; k0 += MOE_K) {
     for (int i = threadIdx.x; i < MOE_TILE * MOE_K; i += 256) {
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                        const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
                        const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
-                       __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, int tile_rows) {
+                       __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
   __shared__ __align__(16) TileMmaSmem s;
   srb_launch_dependents();
   srb_grid_dependency_wait();
@@ -307,7 +307,7 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
   const int col0 = blockIdx.x * MOE_TILE;
-  const size_t matrix = (size_t)expert * n_out * n_in + (size_t)col0 * n_in;
+  const size_t matrix = (size_t)expert * expert_stride + (size_t)col0 * n_in;
   constexpr int NW = GATED ? 2 : 1;
   float acc[NW][2][4][4];
   if (GATED) {
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(256)
 moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                          const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
                          const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
-                         __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f) {
+                         __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, size_t expert_stride) {
   constexpr int NW = GATED ? 2 : 1;
   extern __shared__ __align__(16) unsigned char moe_smem[];
   TileAsyncSmem<NW, ROWS, STAGES>& s = *reinterpret_cast<TileAsyncSmem<NW, ROWS, STAGES>*>(moe_smem);
@@ -356,7 +356,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   if (t < ROWS) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
   const int col0 = blockIdx.x * TA_COLS;
-  const size_t matrix = (size_t)expert * n_out * n_in + (size_t)col0 * n_in;
+  const size_t matrix = (size_t)expert * expert_stride + (size_t)col0 * n_in;
   float acc[NW][2][4][4];
   if (GATED) {
     const __nv_bfloat16* const bases[2] = {w_a + matrix, w_b + matrix};
@@ -396,7 +396,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 template <typename T>
 static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
                                const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
-                               void* out_t, float* out_f, cudaStream_t s) {
+                               void* out_t, float* out_f, size_t expert_stride, cudaStream_t s) {
   const int tile_rows = moe_tile_rows(rows, top, experts);
   dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts), (tile_rows + MOE_TILE - 1) / MOE_TILE);
   if (grid.y > 65535) SRB_FAIL("moe product: %d tiles exceed one launch", (int)grid.y);
@@ -410,7 +410,7 @@ static int launch_moe_products(bool gated, const void* x, const void* w_a, const
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                       \
     SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<GATED, ROWS, STAGES>, grid, dim3(256), smem, s,                  \
                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan,      \
-                             slot_row, experts, n_in, n_out, activation, (__nv_bfloat16*)out_t, out_f));               \
+                             slot_row, experts, n_in, n_out, activation, (__nv_bfloat16*)out_t, out_f, expert_stride)); \
   } while (0)
     if (tile_rows == MOE_FEW_ROWS) {
       if (gated) MOE_ASYNC_LAUNCH(true, MOE_FEW_ROWS, MOE_FEW_STAGES); else MOE_ASYNC_LAUNCH(false, MOE_FEW_ROWS, MOE_FEW_STAGES);
@@ -426,36 +426,37 @@ static int launch_moe_products(bool gated, const void* x, const void* w_a, const
     if (gated)
       SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                                (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows));
+                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride));
     else
       SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                                (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows));
+                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride));
     SRB_LAUNCH_CHECK("moe product");
     return SRB_OK;
   }
   if (gated)
     SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, true>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows));
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride));
   else
     SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, false>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows));
+                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride));
   SRB_LAUNCH_CHECK("moe product");
   return SRB_OK;
 }
 
-// h: [rows, width]; w_gate, w_up: [experts, inner, width]; act: [rows * top, inner]
-extern "C" int srb_moe_gated_up(const void* h, const void* w_gate, const void* w_up, const int* plan, const int* slot_row,
-                                int rows, int top, int experts, int width, int inner, int activation, void* act, int dtype,
-                                void* stream) {
+// h: [rows, width]; w_gate, w_up: expert e's [inner, width] matrix starts expert_stride elements after expert e - 1's
+// (the two may be halves of one stacked tensor); act: [rows * top, inner]
+extern "C" int srb_moe_gated_up(const void* h, const void* w_gate, const void* w_up, long long expert_stride, const int* plan,
+                                const int* slot_row, int rows, int top, int experts, int width, int inner, int activation,
+                                void* act, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_gated_up: sizes %d, %d must be positive", width, inner);
   if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_gated_up: unknown activation %d", activation);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, s);
+    return launch_moe_products<float>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, s);
+    return launch_moe_products<__nv_bfloat16>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
   SRB_FAIL("moe_gated_up: unknown dtype %d", dtype);
 }
 
@@ -466,9 +467,9 @@ extern "C" int srb_moe_down(const void* act, const void* w_down, const int* plan
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_down: sizes %d, %d must be positive", width, inner);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, s);
+    return launch_moe_products<float>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, s);
+    return launch_moe_products<__nv_bfloat16>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
   SRB_FAIL("moe_down: unknown dtype %d", dtype);
 }
 
@@ -495,3 +496,37 @@ extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const floa
   SRB_LAUNCH_CHECK("moe_combine");
   return SRB_OK;
 }
+
+// rows of h in slot order: out[slot, :] = h[slot_row[slot], :] (16 bytes a thread where the rows allow it), for
+// products that take their operands as whole tiles of consecutive rows
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ slot_row, int width, T* __restrict__ out) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int slot = blockIdx.x;
+  const T* src = h + (size_t)slot_row[slot] * width;
+  T* dst = out + (size_t)slot * width;
+  if ((width * sizeof(T)) % 16 == 0 && (((uintptr_t)h | (uintptr_t)out) & 15) == 0) {
+    const int pieces = width * sizeof(T) / 16;
+    for (int i = threadIdx.x; i < pieces; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    return;
+  }
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int srb_moe_gather(const void* h, const int* slot_row, int slots, int width, void* out, int dtype, void* stream) {
+  if (slots <= 0 || width <= 0) return SRB_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(moe_gather_kernel<float>, dim3(slots), dim3(128), 0, s, (const float*)h, slot_row, width, (float*)out));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(moe_gather_kernel<__nv_bfloat16>, dim3(slots), dim3(128), 0, s, (const __nv_bfloat16*)h, slot_row,
+                             width, (__nv_bfloat16*)out));
+  else
+    SRB_FAIL("moe_gather: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("moe_gather");
+  return SRB_OK;
+}
+
+extern "C" int srb_moe_tile_rows(int rows, int top, int experts) { return moe_tile_rows(rows, top, experts); }

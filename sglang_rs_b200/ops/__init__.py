@@ -680,19 +680,29 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
 
 # --------------------------------------------------------------------------- routed experts
 
+#: bfloat16 steps whose plan has tiles of 128 slots run the experts' two products on the grouped mode of the tcgen05
+#: kernel (csrc/gemm_bf16.cu) over rows gathered into slot order; SRB_GROUPED_EXPERTS=0 keeps the mma.sync tiles
+GROUPED_EXPERTS = os.environ.get("SRB_GROUPED_EXPERTS", "1") not in ("0", "off", "false")
+
+
 @traced("routed_experts")
-def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                   top: int, activation: str, renormalize: bool, error_word: torch.Tensor) -> torch.Tensor:
+def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                   activation: str, renormalize: bool, error_word: torch.Tensor) -> torch.Tensor:
     """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].
 
-    ``router`` [experts, width]; ``w_gate``, ``w_up`` [experts, inner, width]; ``w_down`` [experts, width, inner],
-    all of h's dtype.  Scores are a softmax over all experts, in 32-bit; with ``renormalize`` the chosen ones are
-    divided by their sum.  Five launches, nothing decided on the host."""
-    _need(h, "h"); _need(router, "router", h.dtype); _need(w_gate, "w_gate", h.dtype); _need(w_up, "w_up", h.dtype)
-    _need(w_down, "w_down", h.dtype)
+    ``router`` [experts, width]; ``w_gate_up`` [experts, 2 * inner, width] (an expert's gate rows over its up rows);
+    ``w_down`` [experts, width, inner], all of h's dtype.  Scores are a softmax over all experts, in 32-bit; with
+    ``renormalize`` the chosen ones are divided by their sum.  Five launches (six with the gather of the grouped
+    products), nothing decided on the host.
+
+    The two products: float32 and odd sizes on FFMA or 64 x 64 mma tiles; bfloat16 on mma.sync tiles with asynchronous
+    copies, or, where a step has many choices per expert (tiles of 128 slots), on tcgen05 tensor cores through the
+    grouped mode of :func:`gemm_bf16`'s kernel: the rows are gathered into slot order first, so that a tile's operand is
+    128 consecutive rows that TMA can fetch."""
+    _need(h, "h"); _need(router, "router", h.dtype); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
     rows, width = h.shape
-    experts, inner = w_gate.shape[0], w_gate.shape[1]
-    if (router.shape != (experts, width) or w_gate.shape != (experts, inner, width) or w_up.shape != w_gate.shape
+    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    if (router.shape != (experts, width) or w_gate_up.shape != (experts, 2 * inner, width)
             or w_down.shape != (experts, width, inner)):
         raise KernelError("routed_experts: shapes of the router and the experts do not agree")
     lib = load_library("moe")
@@ -711,10 +721,27 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate: torch.Tensor, 
                                   _ptr(weights), code, stream))
     _check(lib, lib.srb_moe_plan(_ptr(chosen), rows, top, experts, _ptr(plan), _ptr(slot_row), _ptr(entry_slot),
                                  _ptr(error_word), stream))
-    _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slot_row), rows, top, experts,
-                                     width, inner, activation_code(activation), _ptr(act), code, stream))
-    _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
-                                 stream))
+    grouped = (GROUPED_EXPERTS and h.dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
+               and lib.srb_moe_tile_rows(rows, top, experts) == 128)
+    if grouped:
+        product = load_library("gemm_bf16")
+        max_tiles = lib.srb_moe_max_tiles(rows, top, experts)
+        gathered = torch.empty((entries, width), dtype=h.dtype, device=device)
+        _check(lib, lib.srb_moe_gather(_ptr(h), _ptr(slot_row), entries, width, _ptr(gathered), code, stream))
+        _check(product, product.srb_gemm_bf16_grouped(
+            _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, entries, experts, 2 * inner, inner, width,
+            inner, inner, GEMM_MODES["gated"], activation_code(activation), _ptr(error_word), stream))
+        _check(product, product.srb_gemm_bf16_grouped(
+            _ptr(act), _ptr(w_down), _ptr(y), _ptr(plan), max_tiles, entries, experts, width, width, inner, width, 0,
+            GEMM_MODES["f32"], 0, _ptr(error_word), stream))
+    else:
+        element = h.element_size()
+        w_up = ctypes.c_void_p(w_gate_up.data_ptr() + inner * width * element)
+        _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate_up), w_up, ctypes.c_longlong(2 * inner * width), _ptr(plan),
+                                         _ptr(slot_row), rows, top, experts, width, inner, activation_code(activation),
+                                         _ptr(act), code, stream))
+        _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
+                                     stream))
     _check(lib, lib.srb_moe_combine(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), stream))
     return out
 

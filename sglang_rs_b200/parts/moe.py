@@ -4,7 +4,7 @@ Router logits z = W_router h in 32-bit, scores s = softmax(z) over all experts; 
 the largest scores are chosen (ties: the lower index) and the result is sum_e s_e * expert_e(h) over the
 chosen ones, with the scores as they are or, with ``renormalize``, divided by their sum.  An expert is a
 gated feed-forward without biases: W_down (act(W_gate h) * (W_up h)).  The experts' matrices are stacked at
-load ([experts, ...]); the whole part is five launches that decide nothing on the host (``ops.routed_experts``),
+load ([experts, ...]; gate rows over up rows); the whole part is a handful of launches that decide nothing on the host (``ops.routed_experts``),
 so decode steps can be captured.  The result is 32-bit: the weighted sum is taken in 32-bit and goes to
 the residual sum (or the norm ahead of it) unrounded.
 """
@@ -33,7 +33,7 @@ class RoutedExperts(FeedForward):
         self.hidden, self.inner, self.experts, self.top = int(hidden), int(inner), int(experts), int(top)
         self.activation, self.router_name, self.renormalize = activation, router_name, bool(renormalize)
         self.names = [expert_names(e) for e in range(self.experts)]
-        self.router = self.w_gate = self.w_up = self.w_down = None
+        self.router = self.w_gate_up = self.w_down = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.router_name: TensorSpec((self.experts, self.hidden))}
@@ -45,10 +45,11 @@ class RoutedExperts(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.router = matrix_to(tensors[self.router_name], device, dtype)
-        self.w_gate = matrix_to(torch.stack([tensors[n.gate] for n in self.names]), device, dtype)
-        self.w_up = matrix_to(torch.stack([tensors[n.up] for n in self.names]), device, dtype)
+        # per expert the gate rows over the up rows: the two matrices of a tile then lie a fixed distance apart
+        self.w_gate_up = matrix_to(torch.stack([torch.cat([tensors[n.gate], tensors[n.up]], dim=0) for n in self.names]),
+                                   device, dtype)
         self.w_down = matrix_to(torch.stack([tensors[n.down] for n in self.names]), device, dtype)
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        return ops.routed_experts(x, self.router, self.w_gate, self.w_up, self.w_down, self.top, self.activation,
+        return ops.routed_experts(x, self.router, self.w_gate_up, self.w_down, self.top, self.activation,
                                   self.renormalize, ctx.error_word)

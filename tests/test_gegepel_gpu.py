@@ -253,8 +253,8 @@ def test_routed_experts(dtype, experts, top, rows):
                         f"p.e{e}.down": torch.randn(width, inner) * 0.2})
     stacked = {n: torch.stack([tensors[f"p.e{e}.{n}"] for e in range(experts)]).to(DEV, dtype) for n in ("gate", "up", "down")}
     word = ops.new_error_word(DEV)
-    out = ops.routed_experts(h.to(DEV, dtype), tensors["p.router"].to(DEV, dtype), stacked["gate"], stacked["up"], stacked["down"],
-                             top, "silu", False, word)
+    out = ops.routed_experts(h.to(DEV, dtype), tensors["p.router"].to(DEV, dtype), torch.cat([stacked["gate"], stacked["up"]], dim=1),
+                             stacked["down"], top, "silu", False, word)
     rounded = {k: seen(v, dtype) for k, v in tensors.items()}
     want = pg.routed_experts(seen(h, dtype), rounded, "p.", {"router": {"experts": experts, "top": top}})
     assert out.dtype == torch.float32 and int(word.item()) == 0
