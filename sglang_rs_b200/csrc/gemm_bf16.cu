@@ -420,14 +420,13 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
 
 // ---- grouped: one weight matrix per expert, tokens grouped by expert ------------------------------------------
 // x [slots, k]: the rows in slot order (the slots of an expert are consecutive); w [experts * expert_rows, k];
-// plan as in GemmArgs, with tiles of 128 slots and room for `max_tiles` of them.  mode 1: out float [slots, ldo] =
+// plan as in GemmArgs, with tiles of `tile_slots` slots (128 or 256) and room for `max_tiles` of them.  mode 1: out float [slots, ldo] =
 // x w_e^T over `features` rows of the expert's matrix; mode 2: the expert's matrix stacks gate rows [0, features) over
 // up rows [up_row_offset, + features), out bf16 [slots, ldo] = act(gate) * up.  Blocks of tiles beyond the plan's
 // count leave at once; rows of a tile behind its expert's last slot are computed and not stored.
-template <int EPI>
+template <int EPI, int BLOCK_T>
 static int launch_grouped(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int max_tiles,
                           cudaStream_t s) {
-  constexpr int BLOCK_T = 128;
   constexpr int STAGE_BYTES = GEMM_BLOCK_F * GEMM_BLOCK_K * 2 + BLOCK_T * GEMM_BLOCK_K * 2;
   constexpr int STAGES = 200 * 1024 / STAGE_BYTES;
   constexpr int FEATURES_PER_BLOCK = EPI == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F;
@@ -441,10 +440,11 @@ static int launch_grouped(const CUtensorMap& map_w, const CUtensorMap& map_x, co
   return SRB_OK;
 }
 
-extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, const int* plan, int max_tiles, int slots,
-                                     int experts, int expert_rows, int features, int k, int ldo, int up_row_offset,
-                                     int mode, int activation, int* error_word, void* stream) {
+extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, const int* plan, int max_tiles, int tile_slots,
+                                     int slots, int experts, int expert_rows, int features, int k, int ldo,
+                                     int up_row_offset, int mode, int activation, int* error_word, void* stream) {
   if (slots <= 0 || features <= 0 || max_tiles <= 0) return SRB_OK;
+  if (tile_slots != 128 && tile_slots != 256) SRB_FAIL("gemm_bf16_grouped: tiles of %d slots are not 128 or 256", tile_slots);
   if (k <= 0 || k % 8 != 0) SRB_FAIL("gemm_bf16_grouped: inner size %d must be a positive multiple of 8", k);
   if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16_grouped: operands must be 16-byte aligned");
   if (mode != EPI_F32 && mode != EPI_SILU) SRB_FAIL("gemm_bf16_grouped: mode %d is not float or gated", mode);
@@ -456,13 +456,16 @@ extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, co
   CUtensorMap map_w, map_x;
   if (make_map(&map_w, w, (long long)experts * expert_rows, k, k, mode == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F) != SRB_OK)
     return SRB_ERR_INVALID;
-  if (make_map(&map_x, x, slots, k, k, 128) != SRB_OK) return SRB_ERR_INVALID;
+  if (make_map(&map_x, x, slots, k, k, tile_slots) != SRB_OK) return SRB_ERR_INVALID;
   GemmArgs args;
   args.out = out; args.tokens = slots; args.features = features; args.k = k; args.ldo = ldo;
   args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
   args.plan = plan; args.experts = experts; args.expert_rows = expert_rows;
   args.k_blocks_per_split = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
   cudaStream_t s = (cudaStream_t)stream;
-  return mode == EPI_SILU ? launch_grouped<EPI_SILU>(map_w, map_x, args, max_tiles, s)
-                          : launch_grouped<EPI_F32>(map_w, map_x, args, max_tiles, s);
+  if (tile_slots == 256)
+    return mode == EPI_SILU ? launch_grouped<EPI_SILU, 256>(map_w, map_x, args, max_tiles, s)
+                            : launch_grouped<EPI_F32, 256>(map_w, map_x, args, max_tiles, s);
+  return mode == EPI_SILU ? launch_grouped<EPI_SILU, 128>(map_w, map_x, args, max_tiles, s)
+                          : launch_grouped<EPI_F32, 128>(map_w, map_x, args, max_tiles, s);
 }

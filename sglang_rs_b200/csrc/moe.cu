@@ -134,6 +134,64 @@ extern "C" int srb_moe_route(const void* h, const void* router, int rows, int wi
   return SRB_OK;
 }
 
+// The choice alone, from logits that a product kernel made (float [rows, experts], `pitch` floats apart): a warp per
+// row does the softmax over all experts and picks the `top` largest as moe_route_kernel does.
+__global__ void moe_select_kernel(const float* __restrict__ logits, size_t pitch, int rows, int experts, int top,
+                                  int renormalize, int* __restrict__ chosen, float* __restrict__ weights) {
+  extern __shared__ float select_scores[];                  // [warps of the block][experts]
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (row >= rows) return;
+  float* score = select_scores + (size_t)warp * experts;
+  const float* z = logits + (size_t)row * pitch;
+  float top_logit = -INFINITY;
+  for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, z[e]);
+  top_logit = srb_warp_max(top_logit);
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    const float p = expf(z[e] - top_logit);
+    score[e] = p;
+    sum += p;
+  }
+  sum = srb_warp_sum(sum);
+  __syncwarp();
+  float kept = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int best_index = experts;
+    for (int e = lane; e < experts; e += 32)
+      if (score[e] > best) { best = score[e]; best_index = e; }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+      if (other > best || (other == best && other_index < best_index)) { best = other; best_index = other_index; }
+    }
+    if (lane == 0) {
+      chosen[(size_t)row * top + k] = best_index;
+      weights[(size_t)row * top + k] = best / sum;
+      score[best_index] = -1.f;
+    }
+    kept += best / sum;
+    __syncwarp();
+  }
+  if (renormalize && lane < top) weights[(size_t)row * top + lane] /= kept;
+}
+
+extern "C" int srb_moe_select(const float* logits, long long pitch, int rows, int experts, int top, int renormalize,
+                              int* chosen, float* weights, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (experts <= 0 || experts > MOE_MAX_EXPERTS) SRB_FAIL("moe_select: %d experts are outside 1 .. %d", experts, MOE_MAX_EXPERTS);
+  if (top <= 0 || top > experts || top > 32) SRB_FAIL("moe_select: %d chosen experts are outside 1 .. min(%d, 32)", top, experts);
+  if (pitch < experts) SRB_FAIL("moe_select: rows of the logits overlap");
+  const int warps = 4;
+  SRB_CUDA_CALL(srb_launch(moe_select_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), (size_t)warps * experts * 4,
+                           (cudaStream_t)stream, logits, (size_t)pitch, rows, experts, top, renormalize, chosen, weights));
+  SRB_LAUNCH_CHECK("moe_select");
+  return SRB_OK;
+}
+
 // One block.  plan: [0] number of tiles, then offsets[experts + 1], then per tile (expert, first slot).
 // slot_row[slot]: the row whose entry sits in the slot; entry_slot[row * top + k]: the slot of that entry.
 __global__ void moe_plan_kernel(const int* __restrict__ chosen, int entries, int top, int experts, int max_tiles,
@@ -194,19 +252,34 @@ extern "C" int srb_moe_plan_ints(int rows, int top, int experts) {
   return 1 + experts + 1 + 2 * max_tiles;
 }
 
+// The same plan with tiles of a size that the caller names (a product kernel with tiles of its own, e.g. 256 slots);
+// the products of this file do not read such a plan.
+extern "C" int srb_moe_plan_ints_of(int rows, int top, int experts, int tile_rows) {
+  return 1 + experts + 1 + 2 * ((rows * top) / tile_rows + experts);
+}
+extern "C" int srb_moe_max_tiles_of(int rows, int top, int experts, int tile_rows) { return (rows * top) / tile_rows + experts; }
+extern "C" int srb_moe_plan_of(const int* chosen, int rows, int top, int experts, int tile_rows, int* plan, int* slot_row,
+                               int* entry_slot, int* error_word, void* stream);
+
 extern "C" int srb_moe_max_tiles(int rows, int top, int experts) {
   return (rows * top) / moe_tile_rows(rows, top, experts) + experts;
 }
 
-extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, int* plan, int* slot_row, int* entry_slot,
-                            int* error_word, void* stream) {
+extern "C" int srb_moe_plan_of(const int* chosen, int rows, int top, int experts, int tile_rows, int* plan, int* slot_row,
+                               int* entry_slot, int* error_word, void* stream) {
   if (rows <= 0) return SRB_OK;
-  if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0) SRB_FAIL("moe_plan: %d experts, %d chosen", experts, top);
+  if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || tile_rows <= 0)
+    SRB_FAIL("moe_plan: %d experts, %d chosen, tiles of %d", experts, top, tile_rows);
   SRB_CUDA_CALL(srb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, chosen, rows * top, top, experts,
-                           srb_moe_max_tiles(rows, top, experts), moe_tile_rows(rows, top, experts), plan, slot_row,
-                           entry_slot, error_word));
+                           (rows * top) / tile_rows + experts, tile_rows, plan, slot_row, entry_slot, error_word));
   SRB_LAUNCH_CHECK("moe_plan");
   return SRB_OK;
+}
+
+extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, int* plan, int* slot_row, int* entry_slot,
+                            int* error_word, void* stream) {
+  return srb_moe_plan_of(chosen, rows, top, experts, moe_tile_rows(rows, top, experts), plan, slot_row, entry_slot, error_word,
+                         stream);
 }
 
 // Half a tile (up to 64 slots of one expert; blockIdx.z names the half) times 64 output columns.  GATED: two weight matrices (gate, up), rows of

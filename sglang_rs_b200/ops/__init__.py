@@ -680,9 +680,14 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
 
 # --------------------------------------------------------------------------- routed experts
 
-#: bfloat16 steps whose plan has tiles of 128 slots run the experts' two products on the grouped mode of the tcgen05
+#: bfloat16 steps with many choices per expert run the experts' two products on the grouped mode of the tcgen05
 #: kernel (csrc/gemm_bf16.cu) over rows gathered into slot order; SRB_GROUPED_EXPERTS=0 keeps the mma.sync tiles
 GROUPED_EXPERTS = os.environ.get("SRB_GROUPED_EXPERTS", "1") not in ("0", "off", "false")
+#: from this many rows on the router's logits come from the product kernels (every block of the fused router kernel reads
+#: the whole router matrix: 94 us at 2,048 rows and 64 experts of width 2,048 against the product's few)
+ROUTER_PRODUCT_MIN_ROWS = 128
+#: slots of a tile of the grouped products (128 or 256): 256 reads an expert's weight tile once for twice as many rows
+GROUPED_TILE_SLOTS = int(os.environ.get("SRB_GROUPED_TILE_SLOTS", "256"))
 
 
 @traced("routed_experts")
@@ -710,29 +715,36 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     entries = rows * top
     chosen = torch.empty(entries, dtype=torch.int32, device=device)
     weights = torch.empty(entries, dtype=torch.float32, device=device)
-    plan = torch.empty(lib.srb_moe_plan_ints(rows, top, experts), dtype=torch.int32, device=device)
+    grouped = (GROUPED_EXPERTS and h.dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
+               and lib.srb_moe_tile_rows(rows, top, experts) == 128)
+    tile_slots = GROUPED_TILE_SLOTS if grouped else lib.srb_moe_tile_rows(rows, top, experts)
+    plan = torch.empty(lib.srb_moe_plan_ints_of(rows, top, experts, tile_slots), dtype=torch.int32, device=device)
     slot_row = torch.empty(entries, dtype=torch.int32, device=device)
     entry_slot = torch.empty(entries, dtype=torch.int32, device=device)
     act = torch.empty((entries, inner), dtype=h.dtype, device=device)
     y = torch.empty((entries, width), dtype=torch.float32, device=device)
     out = torch.empty((rows, width), dtype=torch.float32, device=device)
     code, stream = dtype_code(h.dtype), _stream()
-    _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, experts, top, int(renormalize), _ptr(chosen),
-                                  _ptr(weights), code, stream))
-    _check(lib, lib.srb_moe_plan(_ptr(chosen), rows, top, experts, _ptr(plan), _ptr(slot_row), _ptr(entry_slot),
-                                 _ptr(error_word), stream))
-    grouped = (GROUPED_EXPERTS and h.dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
-               and lib.srb_moe_tile_rows(rows, top, experts) == 128)
+    if rows >= ROUTER_PRODUCT_MIN_ROWS:
+        # many rows: the logits are a product like any other (32-bit accumulation, 32-bit result), the choice a kernel of its own
+        logits = linear(h, router, out_dtype=torch.float32, error_word=error_word)
+        _check(lib, lib.srb_moe_select(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, experts, top, int(renormalize),
+                                       _ptr(chosen), _ptr(weights), stream))
+    else:
+        _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, experts, top, int(renormalize), _ptr(chosen),
+                                      _ptr(weights), code, stream))
+    _check(lib, lib.srb_moe_plan_of(_ptr(chosen), rows, top, experts, tile_slots, _ptr(plan), _ptr(slot_row),
+                                    _ptr(entry_slot), _ptr(error_word), stream))
     if grouped:
         product = load_library("gemm_bf16")
-        max_tiles = lib.srb_moe_max_tiles(rows, top, experts)
+        max_tiles = lib.srb_moe_max_tiles_of(rows, top, experts, tile_slots)
         gathered = torch.empty((entries, width), dtype=h.dtype, device=device)
         _check(lib, lib.srb_moe_gather(_ptr(h), _ptr(slot_row), entries, width, _ptr(gathered), code, stream))
         _check(product, product.srb_gemm_bf16_grouped(
-            _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, entries, experts, 2 * inner, inner, width,
+            _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, tile_slots, entries, experts, 2 * inner, inner, width,
             inner, inner, GEMM_MODES["gated"], activation_code(activation), _ptr(error_word), stream))
         _check(product, product.srb_gemm_bf16_grouped(
-            _ptr(act), _ptr(w_down), _ptr(y), _ptr(plan), max_tiles, entries, experts, width, width, inner, width, 0,
+            _ptr(act), _ptr(w_down), _ptr(y), _ptr(plan), max_tiles, tile_slots, entries, experts, width, width, inner, width, 0,
             GEMM_MODES["f32"], 0, _ptr(error_word), stream))
     else:
         element = h.element_size()
