@@ -4,6 +4,9 @@
 //
 //   SRB_ACT_SILU       g / (1 + exp(-g))                     (crates/sglang-kernel/src/cpu.rs:119-123)
 //   SRB_ACT_GELU_TANH  g/2 * (1 + tanh(sqrt(2/pi) * (g + 0.044715 g^3)))
+//   SRB_ACT_RELU2      max(g, 0)^2
+//
+// A feed-forward without a gate calls the same function with u = 1.
 //
 // EXACT selects the full-precision exponential and division (the 32-bit path and epilogues whose
 // result stays 32-bit); without it the hardware's approximations are used, which is exact enough for
@@ -12,10 +15,15 @@
 
 #define SRB_ACT_SILU 0
 #define SRB_ACT_GELU_TANH 1
-#define SRB_ACT_COUNT 2
+#define SRB_ACT_RELU2 2
+#define SRB_ACT_COUNT 3
 
 template <bool EXACT>
 __device__ __forceinline__ float srb_gated(int activation, float g, float u) {
+  if (activation == SRB_ACT_RELU2) {
+    const float r = fmaxf(g, 0.f);
+    return r * r * u;
+  }
   if (activation == SRB_ACT_GELU_TANH) {
     const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
     // tanh(x) = 1 - 2 / (exp(2x) + 1): finite for every x

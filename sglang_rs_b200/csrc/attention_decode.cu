@@ -39,7 +39,7 @@ struct DecodeParams {
 
 __device__ __forceinline__ void decode_units(const AttnParams& p, int pos, int& first_unit, int& units, int& lo,
                                              int& hi) {
-  lo = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+  lo = srb_first_visible(pos, p.window, p.chunk);
   hi = pos + 1;
   first_unit = lo / DEC_UNIT;
   units = (hi - 1) / DEC_UNIT - first_unit + 1;
@@ -418,12 +418,14 @@ extern "C" int srb_decode_attention_supports(int n_q, int n_kv, int head_dim, in
 // token.  `num_splits` blocks share the keys of a (row, kv head); scratch: part_acc holds
 // rows * n_q * num_splits * head_dim floats, part_ml rows * n_q * num_splits * 2; `counters` holds
 // rows * n_kv ints that are zero before the call and zero again after it.
-extern "C" int srb_decode_attention(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                    float* part_acc, float* part_ml, int* counters, const int* positions,
-                                    const int* row_request, const int* block_table, int table_stride, int rows,
-                                    int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                    int num_splits, float scale, int* error_word, void* stream) {
+// `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
+extern "C" int srb_decode_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           float* part_acc, float* part_ml, int* counters, const int* positions,
+                                           const int* row_request, const int* block_table, int table_stride, int rows,
+                                           int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                           int chunk, int num_splits, float scale, int* error_word, void* stream) {
   if (rows <= 0) return SRB_OK;
+  if (chunk < 0) SRB_FAIL("decode_attention: the chunk size must be non-negative");
   if (!srb_decode_attention_supports(n_q, n_kv, head_dim, SRB_DTYPE_BF16))
     SRB_FAIL("decode_attention: head_dim %d (64 or 128) or %d query heads per kv head (at most 16) is not taken "
              "by this kernel", head_dim, n_kv > 0 ? n_q / n_kv : 0);
@@ -435,10 +437,20 @@ extern "C" int srb_decode_attention(const void* q, const void* k_pool, const voi
   AttnParams& p = dp.a;
   p.positions = positions; p.row_request = row_request; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
-  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.split_size = 0;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = 0;
   p.max_splits = num_splits; p.scale = scale; p.error_word = error_word;
   dp.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   if (head_dim == 64) return launch_decode<64>(q, k_pool, v_pool, out, part_acc, part_ml, counters, dp, rows, s);
   return launch_decode<128>(q, k_pool, v_pool, out, part_acc, part_ml, counters, dp, rows, s);
+}
+
+extern "C" int srb_decode_attention(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                    float* part_acc, float* part_ml, int* counters, const int* positions,
+                                    const int* row_request, const int* block_table, int table_stride, int rows,
+                                    int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                    int num_splits, float scale, int* error_word, void* stream) {
+  return srb_decode_attention_masked(q, k_pool, v_pool, out, part_acc, part_ml, counters, positions, row_request,
+                                     block_table, table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, 0,
+                                     num_splits, scale, error_word, stream);
 }

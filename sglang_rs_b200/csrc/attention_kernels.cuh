@@ -40,6 +40,7 @@ struct AttnParams {
   int table_stride;
   int n_q, n_kv, head_dim, page_size, num_pages;
   int window;                // 0 = all keys
+  int chunk;                 // > 0: a row sees only the keys of its own chunk of `chunk` positions, counted from position 0
   int split_size;            // 0 = no split
   int max_splits;
   float scale;
@@ -51,8 +52,19 @@ struct AttnParams {
   int heads_per_block;
 };
 
+// The first key that a row at `pos` may see: the start of its window, or of its chunk of positions, whichever is later.
+// It never falls as pos grows, so the first row of a tile has the lowest first key of the tile.
+__host__ __device__ __forceinline__ int srb_first_visible(int pos, int window, int chunk) {
+  int begin = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  if (chunk > 0) {
+    const int start = pos / chunk * chunk;
+    begin = begin > start ? begin : start;
+  }
+  return begin;
+}
+
 __device__ __forceinline__ void row_key_range(const AttnParams& p, int pos, int split, int& lo, int& hi) {
-  const int begin = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+  const int begin = srb_first_visible(pos, p.window, p.chunk);
   const int end = pos + 1;
   if (p.split_size == 0) {
     lo = begin;
@@ -66,7 +78,7 @@ __device__ __forceinline__ void row_key_range(const AttnParams& p, int pos, int 
 
 __device__ __forceinline__ int row_split_count(const AttnParams& p, int pos) {
   if (p.split_size == 0) return 1;
-  const int begin = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;
+  const int begin = srb_first_visible(pos, p.window, p.chunk);
   return pos / p.split_size - begin / p.split_size + 1;
 }
 
@@ -244,13 +256,15 @@ static int launch_attention(const void* q, const void* k_pool, const void* v_poo
 // part_acc holds rows * n_q * max_splits * value_dim floats and part_ml rows * n_q * max_splits * 2.
 // `sinks` null: no sink.  `value_dim` 0: as wide as the keys.  `v_pool` null: the values are the first
 // value_dim entries of the key rows.
-static int paged_attention_dispatch_ex(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                       float* part_acc, float* part_ml, const int* positions,
-                                       const int* row_request, const int* block_table, int table_stride, int rows,
-                                       int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                       int split_size, int max_splits, float scale, int* error_word, int dtype,
-                                       const float* sinks, int value_dim, void* stream) {
+// `chunk` > 0: a row sees only keys of its own chunk of positions (see AttnParams).
+static int paged_attention_dispatch_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           float* part_acc, float* part_ml, const int* positions,
+                                           const int* row_request, const int* block_table, int table_stride, int rows,
+                                           int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                           int chunk, int split_size, int max_splits, float scale, int* error_word,
+                                           int dtype, const float* sinks, int value_dim, void* stream) {
   if (rows <= 0) return SRB_OK;
+  if (chunk < 0) SRB_FAIL("paged_attention: the chunk size must be non-negative");
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0)
     SRB_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
   if (head_dim <= 0) SRB_FAIL("paged_attention: head_dim %d must be positive", head_dim);
@@ -270,7 +284,7 @@ static int paged_attention_dispatch_ex(const void* q, const void* k_pool, const 
   AttnParams p;
   p.positions = positions; p.row_request = row_request; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
-  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.split_size = split_size;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = split_size;
   p.max_splits = split_size == 0 ? 1 : max_splits; p.scale = scale; p.error_word = error_word;
   p.sinks = sinks; p.value_dim = value_dim; p.shared_values = v_pool == nullptr;
   const int groups = n_q / n_kv;
@@ -290,6 +304,17 @@ static int paged_attention_dispatch_ex(const void* q, const void* k_pool, const 
   if (dtype == SRB_DTYPE_F32) { SRB_ATTN_DISPATCH(float) }
   if (dtype == SRB_DTYPE_BF16) { SRB_ATTN_DISPATCH(__nv_bfloat16) }
   SRB_FAIL("paged_attention: unknown dtype %d", dtype);
+}
+
+static int paged_attention_dispatch_ex(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                       float* part_acc, float* part_ml, const int* positions,
+                                       const int* row_request, const int* block_table, int table_stride, int rows,
+                                       int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                       int split_size, int max_splits, float scale, int* error_word, int dtype,
+                                       const float* sinks, int value_dim, void* stream) {
+  return paged_attention_dispatch_masked(q, k_pool, v_pool, out, part_acc, part_ml, positions, row_request, block_table,
+                                         table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, 0,
+                                         split_size, max_splits, scale, error_word, dtype, sinks, value_dim, stream);
 }
 
 static int paged_attention_dispatch(const void* q, const void* k_pool, const void* v_pool, void* out,

@@ -46,7 +46,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int kv_head = head / groups;
   const int row_begin = tiles[4 * tile], n_rows = tiles[4 * tile + 1];
   const int request = tiles[4 * tile + 2], pos_begin = tiles[4 * tile + 3];
-  const int kv_lo = (p.window > 0 && pos_begin + 1 > p.window) ? pos_begin + 1 - p.window : 0;
+  const int kv_lo = srb_first_visible(pos_begin, p.window, p.chunk);
   const int kv_hi = pos_begin + n_rows;                                  // keys 0 .. last row's position
   const int first_block = kv_lo / PF_KEYS, last_block = (kv_hi - 1) / PF_KEYS;
 
@@ -91,8 +91,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   // rows of this thread inside the tile and their positions
   const int r_in[2] = {warp * 16 + g, warp * 16 + g + 8};
   const int pos_r[2] = {pos_begin + r_in[0], pos_begin + r_in[1]};
-  const int lowest_r[2] = {(p.window > 0 && pos_r[0] + 1 > p.window) ? pos_r[0] + 1 - p.window : 0,
-                           (p.window > 0 && pos_r[1] + 1 > p.window) ? pos_r[1] + 1 - p.window : 0};
+  const int lowest_r[2] = {srb_first_visible(pos_r[0], p.window, p.chunk), srb_first_visible(pos_r[1], p.window, p.chunk)};
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const int warp_first_pos = pos_begin + warp * 16;
   const int warp_last_pos = pos_begin + min(warp * 16 + 15, n_rows - 1);
@@ -124,7 +123,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __syncthreads();
     const int block_lo = block * PF_KEYS, block_hi = block_lo + PF_KEYS;
     // the block matters to this warp if some key in it is visible to one of the warp's rows
-    const int warp_window_lo = (p.window > 0 && warp_first_pos + 1 > p.window) ? warp_first_pos + 1 - p.window : 0;
+    const int warp_window_lo = srb_first_visible(warp_first_pos, p.window, p.chunk);
     if (warp_has_rows && block_lo <= warp_last_pos && block_hi > warp_window_lo) {
       const __nv_bfloat16* ks = kv + (size_t)stage * 2 * PF_KEYS * D;
       const __nv_bfloat16* vs = ks + PF_KEYS * D;
@@ -149,7 +148,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       // the comparisons.
       float mx[2] = {-INFINITY, -INFINITY};
       const bool all_visible = warp * 16 + 15 < n_rows && block_hi - 1 <= warp_first_pos &&
-                               (p.window == 0 || block_lo >= pos_begin + warp * 16 + 15 + 1 - p.window);
+                               block_lo >= srb_first_visible(pos_begin + warp * 16 + 15, p.window, p.chunk);
       if (all_visible) {
 #pragma unroll
         for (int t = 0; t < NT_S; ++t) {
@@ -257,11 +256,13 @@ extern "C" int srb_prefill_attention_supports(int n_q, int n_kv, int head_dim, i
 extern "C" int srb_prefill_tile_rows() { return PF_ROWS; }
 
 // q, out: [rows, n_q, head_dim] of the whole step; tiles: [num_tiles, 4] ints (see the top).
-extern "C" int srb_prefill_attention(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                     const int* tiles, int num_tiles, const int* block_table, int table_stride,
-                                     int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                     float scale, int* error_word, void* stream) {
+// `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
+extern "C" int srb_prefill_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                            const int* tiles, int num_tiles, const int* block_table, int table_stride,
+                                            int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                            int chunk, float scale, int* error_word, void* stream) {
   if (num_tiles <= 0) return SRB_OK;
+  if (chunk < 0) SRB_FAIL("prefill_attention: the chunk size must be non-negative");
   if (!srb_prefill_attention_supports(n_q, n_kv, head_dim, SRB_DTYPE_BF16))
     SRB_FAIL("prefill_attention: head_dim %d is not 64 or 128, or %d query heads are no multiple of %d kv heads",
              head_dim, n_q, n_kv);
@@ -270,9 +271,17 @@ extern "C" int srb_prefill_attention(const void* q, const void* k_pool, const vo
   AttnParams p;
   p.positions = nullptr; p.row_request = nullptr; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
-  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.split_size = 0;
+  p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = 0;
   p.max_splits = 1; p.scale = scale; p.error_word = error_word;
   cudaStream_t s = (cudaStream_t)stream;
   if (head_dim == 64) return launch_prefill<64>(q, k_pool, v_pool, out, tiles, num_tiles, p, s);
   return launch_prefill<128>(q, k_pool, v_pool, out, tiles, num_tiles, p, s);
+}
+
+extern "C" int srb_prefill_attention(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                     const int* tiles, int num_tiles, const int* block_table, int table_stride,
+                                     int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                     float scale, int* error_word, void* stream) {
+  return srb_prefill_attention_masked(q, k_pool, v_pool, out, tiles, num_tiles, block_table, table_stride, n_q, n_kv,
+                                      head_dim, page_size, num_pages, window, 0, scale, error_word, stream);
 }

@@ -40,7 +40,7 @@ struct TcArgs {
   const int* tiles;
   const int* block_table;
   __nv_bfloat16* out;
-  int table_stride, n_q, n_kv, page_size, pool_rows, window;
+  int table_stride, n_q, n_kv, page_size, pool_rows, window, chunk;
   float scale_log2;
   int* error_word;
 };
@@ -130,7 +130,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int kv_head = head0 / groups;
   const int row_begin = args.tiles[4 * tile], n_rows = args.tiles[4 * tile + 1];
   const int request = args.tiles[4 * tile + 2], pos_begin = args.tiles[4 * tile + 3];
-  const int kv_lo = (args.window > 0 && pos_begin + 1 > args.window) ? pos_begin + 1 - args.window : 0;
+  const int kv_lo = srb_first_visible(pos_begin, args.window, args.chunk);
   const int kv_hi = pos_begin + n_rows;
   const int first_block = kv_lo / TC_KEYS, last_block = (kv_hi - 1) / TC_KEYS;
   const int num_blocks = last_block - first_block + 1;
@@ -283,7 +283,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int pos_r = pos_begin + r;
-    const int lowest_r = (args.window > 0 && pos_r + 1 > args.window) ? pos_r + 1 - args.window : 0;
+    const int lowest_r = srb_first_visible(pos_r, args.window, args.chunk);
     const bool row_live = r < n_rows;
     const unsigned lane_address = tmem_base + t * HEAD_COLUMNS + ((unsigned)(quarter * 32) << 16);
     float m_run = -INFINITY, l_run = 0.f;
@@ -295,7 +295,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_after();
       const int key0 = (first_block + i) * TC_KEYS;
       const bool all_visible = n_rows == TC_ROWS && key0 + TC_KEYS - 1 <= pos_begin &&
-                               (args.window == 0 || key0 >= pos_begin + TC_ROWS - args.window);
+                               key0 >= srb_first_visible(pos_begin + TC_ROWS - 1, args.window, args.chunk);
       // the row's 64 raw scores, once; masked keys become -inf
       float sv[TC_KEYS];
       tmem_load_64(lane_address + s_col, sv);
@@ -476,11 +476,14 @@ static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const C
 
 // q, out: [rows, n_q, head_dim] bfloat16 of the whole step; pools [pages, n_kv, page_size, head_dim];
 // tiles: [num_tiles, 4] ints with at most 128 rows each.
-extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                        const int* tiles, int num_tiles, int rows, const int* block_table,
-                                        int table_stride, int n_q, int n_kv, int head_dim, int page_size,
-                                        int num_pages, int window, float scale, int* error_word, void* stream) {
+// `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
+extern "C" int srb_prefill_attention_tc_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                               const int* tiles, int num_tiles, int rows, const int* block_table,
+                                               int table_stride, int n_q, int n_kv, int head_dim, int page_size,
+                                               int num_pages, int window, int chunk, float scale, int* error_word,
+                                               void* stream) {
   if (num_tiles <= 0) return SRB_OK;
+  if (chunk < 0) SRB_FAIL("prefill_attention_tc: the chunk size must be non-negative");
   if (!srb_prefill_tc_supports(n_q, n_kv, head_dim, page_size, SRB_DTYPE_BF16))
     SRB_FAIL("prefill_attention_tc: head_dim %d (64 or 128), page size %d (a multiple of 8 dividing 64) or the "
              "head counts are not taken by this kernel", head_dim, page_size);
@@ -517,7 +520,7 @@ extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const
   }
   TcArgs args;
   args.tiles = tiles; args.block_table = block_table; args.out = (__nv_bfloat16*)out; args.table_stride = table_stride;
-  args.n_q = n_q; args.n_kv = n_kv; args.page_size = page_size; args.pool_rows = (int)pool_rows; args.window = window;
+  args.n_q = n_q; args.n_kv = n_kv; args.page_size = page_size; args.pool_rows = (int)pool_rows; args.window = window; args.chunk = chunk;
   args.scale_log2 = scale * 1.4426950408889634f; args.error_word = error_word;
   cudaStream_t s = (cudaStream_t)stream;
   // two query heads per block when the heads of a kv head pair up
@@ -527,4 +530,12 @@ extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const
                  : launch_tc<64, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
   return pairs ? launch_tc<128, 2, 4>(map_q, map_k, map_v, map_out, args, num_tiles, s)
                : launch_tc<128, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
+}
+
+extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        const int* tiles, int num_tiles, int rows, const int* block_table,
+                                        int table_stride, int n_q, int n_kv, int head_dim, int page_size,
+                                        int num_pages, int window, float scale, int* error_word, void* stream) {
+  return srb_prefill_attention_tc_masked(q, k_pool, v_pool, out, tiles, num_tiles, rows, block_table, table_stride, n_q,
+                                         n_kv, head_dim, page_size, num_pages, window, 0, scale, error_word, stream);
 }

@@ -46,6 +46,7 @@ SRB_DEFINE_PDL_SWITCH()
 #define EPI_SILU 2
 #define EPI_PARTIAL 3
 #define EPI_ADD 4          // out (float) += sum over the K splits, reduced inside a cluster
+#define EPI_ACT 5          // out (bfloat16) = activation(x w^T): a feed-forward's first product without a gate
 
 // Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = tokens.
 __host__ __device__ constexpr unsigned instruction_descriptor(int n) {
@@ -250,6 +251,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (token >= token_limit) break;
           if (EPI == EPI_BF16) {
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] = __float2bfloat16_rn(acc[j]);
+          } else if (EPI == EPI_ACT) {
+            reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
+                __float2bfloat16_rn(srb_gated<true>(args.activation, acc[j], 1.0f));
           } else if (EPI == EPI_F32) {
             reinterpret_cast<float*>(args.out)[(size_t)token * args.ldo + feature] = acc[j];
           } else {
@@ -370,6 +374,7 @@ extern "C" int srb_gemm_bf16_block_tokens(int tokens, int mode) {
 // mode 2: w stacks gate rows [0, features) and up rows [up_row_offset, up_row_offset + features);
 //         out bf16 [tokens, ldo] = act(x gate^T) * (x up^T), act being SRB_ACT_* `activation` (activations.cuh).
 // mode 3: `splits` partial sums over K as float [splits, tokens, ldo]; the caller adds them in order.
+// mode 5: out bf16 [tokens, ldo] = activation(x w^T).
 // mode 4: out float [tokens, ldo] += x w^T, K cut into `splits` (at most 8) blocks that form a cluster and add
 //         their sums in block order.
 extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
@@ -380,8 +385,8 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
     SRB_FAIL("gemm_bf16: inner size %d and the row pitches %d, %d must be positive multiples of 8 (16-byte rows "
              "for TMA)", k, ldx, ldw);
   if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16: operands must be 16-byte aligned");
-  if (mode < 0 || mode > 4) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
-  if (mode == EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT))
+  if (mode < 0 || mode > 5) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
+  if ((mode == EPI_SILU || mode == EPI_ACT) && (activation < 0 || activation >= SRB_ACT_COUNT))
     SRB_FAIL("gemm_bf16: unknown activation %d", activation);
   if (ldo < features) SRB_FAIL("gemm_bf16: output pitch %d is smaller than %d features", ldo, features);
   if (mode == EPI_SILU && up_row_offset + features > rows_of_w)
@@ -413,6 +418,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
     case EPI_F32: return dispatch_tokens<EPI_F32>(block_t, map_w, map_x, args, splits, s);
     case EPI_SILU: return dispatch_tokens<EPI_SILU>(block_t, map_w, map_x, args, 1, s);
     case EPI_ADD: return dispatch_tokens<EPI_ADD>(block_t, map_w, map_x, args, splits, s);
+    case EPI_ACT: return dispatch_tokens<EPI_ACT>(block_t, map_w, map_x, args, 1, s);
     default: return dispatch_tokens<EPI_PARTIAL>(block_t, map_w, map_x, args, splits, s);
   }
 }
@@ -447,8 +453,9 @@ extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, co
   if (tile_slots != 128 && tile_slots != 256) SRB_FAIL("gemm_bf16_grouped: tiles of %d slots are not 128 or 256", tile_slots);
   if (k <= 0 || k % 8 != 0) SRB_FAIL("gemm_bf16_grouped: inner size %d must be a positive multiple of 8", k);
   if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16_grouped: operands must be 16-byte aligned");
-  if (mode != EPI_F32 && mode != EPI_SILU) SRB_FAIL("gemm_bf16_grouped: mode %d is not float or gated", mode);
-  if (mode == EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT)) SRB_FAIL("gemm_bf16_grouped: unknown activation %d", activation);
+  if (mode != EPI_F32 && mode != EPI_SILU && mode != EPI_ACT)
+    SRB_FAIL("gemm_bf16_grouped: mode %d is not float, gated or activated", mode);
+  if (mode != EPI_F32 && (activation < 0 || activation >= SRB_ACT_COUNT)) SRB_FAIL("gemm_bf16_grouped: unknown activation %d", activation);
   if (!plan || experts <= 0 || expert_rows <= 0) SRB_FAIL("gemm_bf16_grouped: a plan and the experts' sizes are needed");
   if ((mode == EPI_SILU ? up_row_offset + features : features) > expert_rows)
     SRB_FAIL("gemm_bf16_grouped: %d features do not fit the %d rows of an expert", features, expert_rows);
@@ -464,8 +471,10 @@ extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, co
   args.k_blocks_per_split = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
   cudaStream_t s = (cudaStream_t)stream;
   if (tile_slots == 256)
-    return mode == EPI_SILU ? launch_grouped<EPI_SILU, 256>(map_w, map_x, args, max_tiles, s)
-                            : launch_grouped<EPI_F32, 256>(map_w, map_x, args, max_tiles, s);
-  return mode == EPI_SILU ? launch_grouped<EPI_SILU, 128>(map_w, map_x, args, max_tiles, s)
-                          : launch_grouped<EPI_F32, 128>(map_w, map_x, args, max_tiles, s);
+    return mode == EPI_SILU  ? launch_grouped<EPI_SILU, 256>(map_w, map_x, args, max_tiles, s)
+           : mode == EPI_ACT ? launch_grouped<EPI_ACT, 256>(map_w, map_x, args, max_tiles, s)
+                             : launch_grouped<EPI_F32, 256>(map_w, map_x, args, max_tiles, s);
+  return mode == EPI_SILU  ? launch_grouped<EPI_SILU, 128>(map_w, map_x, args, max_tiles, s)
+         : mode == EPI_ACT ? launch_grouped<EPI_ACT, 128>(map_w, map_x, args, max_tiles, s)
+                           : launch_grouped<EPI_F32, 128>(map_w, map_x, args, max_tiles, s);
 }

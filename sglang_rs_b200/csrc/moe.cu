@@ -7,6 +7,7 @@
 //   srb_moe_plan      groups the (row, choice) entries by expert: a slot for each entry, the row of each slot, the
 //                     first slot of each expert, and the list of row tiles that the two products walk
 //   srb_moe_gated_up  act[slot, :] = activation(W_gate[e] h[row]) * (W_up[e] h[row])   for the slot's expert and row
+//   srb_moe_act_up    act[slot, :] = activation(W_up[e] h[row])                        (experts without a gate)
 //   srb_moe_down      y[slot, :]   = W_down[e] act[slot]                              (32-bit result)
 //   srb_moe_combine   out[row, :]  = sum over the row's choices, in their order, of weight * y[slot]   (32-bit)
 //
@@ -284,12 +285,17 @@ extern "C" int srb_moe_plan(const int* chosen, int rows, int top, int experts, i
 
 // Half a tile (up to 64 slots of one expert; blockIdx.z names the half) times 64 output columns.  GATED: two weight matrices (gate, up), rows of
 // x gathered through slot_row, result act(gate) * up in T.  Otherwise one matrix, rows of x are the slots
-// themselves, result in float.
-template <typename T, bool GATED>
+// themselves, result in float.  MODE: MOE_DOWN (one matrix, rows are the slots, float result), MOE_GATED (two matrices,
+// rows gathered, act(gate) * up in T), MOE_ACT (one matrix, rows gathered, act(product) in T).
+#define MOE_DOWN 0
+#define MOE_GATED 1
+#define MOE_ACT 2
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b,
                    const int* __restrict__ plan, const int* __restrict__ slot_row, int experts, int n_in, int n_out,
                    int activation, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
+  constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   __shared__ float x_tile[MOE_K][MOE_TILE + 4];
   __shared__ float a_tile[MOE_K][MOE_TILE + 4];
   __shared__ float b_tile[GATED ? MOE_K : 1][MOE_TILE + 4];
@@ -304,7 +310,7 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
   const int count = min(min(MOE_TILE, tile_rows - MOE_TILE * (int)blockIdx.z), offsets[expert + 1] - first);
   if (count <= 0) return;
   const int t = threadIdx.x;
-  if (t < MOE_TILE) tile_row[t] = t < count ? (GATED ? slot_row[first + t] : first + t) : -1;
+  if (t < MOE_TILE) tile_row[t] = t < count ? (GATHER ? slot_row[first + t] : first + t) : -1;
   __syncthreads();
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int col0 = blockIdx.x * MOE_TILE;
@@ -353,6 +359,8 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
       if (c >= n_out) continue;
       if (GATED)
         out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], acc_b[i][j]));
+      else if (MODE == MOE_ACT)
+        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], 1.0f));
       else
         out_f[slot * n_out + c] = acc_a[i][j];
     }
@@ -360,12 +368,13 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
 }
 
 // The same tile on the tensor cores (bfloat16): tile_mma.cuh.
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                        const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
                        const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
                        __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
+  constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   __shared__ __align__(16) TileMmaSmem s;
   srb_launch_dependents();
   srb_grid_dependency_wait();
@@ -377,7 +386,7 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   const int count = min(min(MOE_TILE, tile_rows - MOE_TILE * (int)blockIdx.z), offsets[expert + 1] - first);
   if (count <= 0) return;
   const int t = threadIdx.x;
-  if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
+  if (t < MOE_TILE) s.a_row[t] = t < count ? x + (size_t)(GATHER ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
   const int col0 = blockIdx.x * MOE_TILE;
   const size_t matrix = (size_t)expert * expert_stride + (size_t)col0 * n_in;
@@ -401,6 +410,8 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
         const size_t at = ((size_t)first + r) * n_out + col;
         if (GATED)
           out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c]));
+        else if (MODE == MOE_ACT)
+          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], 1.0f));
         else
           out_f[at] = acc[0][i][j][c];
       }
@@ -408,12 +419,13 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 
 // A whole tile (up to 128 slots) times 64 output columns, operands through a ring of asynchronous copies
 // (tile_mma.cuh); for rows that start on 16-byte boundaries.
-template <bool GATED, int ROWS, int STAGES>
+template <int MODE, int ROWS, int STAGES>
 __global__ void __launch_bounds__(256)
 moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                          const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
                          const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
                          __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, size_t expert_stride) {
+  constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   constexpr int NW = GATED ? 2 : 1;
   extern __shared__ __align__(16) unsigned char moe_smem[];
   TileAsyncSmem<NW, ROWS, STAGES>& s = *reinterpret_cast<TileAsyncSmem<NW, ROWS, STAGES>*>(moe_smem);
@@ -426,7 +438,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   const int expert = tiles[2 * tile], first = tiles[2 * tile + 1];
   const int count = min(ROWS, offsets[expert + 1] - first);
   const int t = threadIdx.x;
-  if (t < ROWS) s.a_row[t] = t < count ? x + (size_t)(GATED ? slot_row[first + t] : first + t) * n_in : nullptr;
+  if (t < ROWS) s.a_row[t] = t < count ? x + (size_t)(GATHER ? slot_row[first + t] : first + t) * n_in : nullptr;
   __syncthreads();
   const int col0 = blockIdx.x * TA_COLS;
   const size_t matrix = (size_t)expert * expert_stride + (size_t)col0 * n_in;
@@ -448,9 +460,9 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         if (r >= count || col >= n_out) continue;
         const size_t at = ((size_t)first + r) * n_out + col;
         const bool pair = col + 1 < n_out;
-        if (GATED) {
-          const float lo = srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c]);
-          const float hi = srb_gated<true>(activation, acc[0][i][j][c + 1], acc[NW - 1][i][j][c + 1]);
+        if (MODE != MOE_DOWN) {
+          const float lo = srb_gated<true>(activation, acc[0][i][j][c], GATED ? acc[NW - 1][i][j][c] : 1.0f);
+          const float hi = srb_gated<true>(activation, acc[0][i][j][c + 1], GATED ? acc[NW - 1][i][j][c + 1] : 1.0f);
           if (pair && (at & 1) == 0) {
             *reinterpret_cast<unsigned*>(out_t + at) = pack_bf16(lo, hi);
           } else {
@@ -467,7 +479,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 }
 
 template <typename T>
-static int launch_moe_products(bool gated, const void* x, const void* w_a, const void* w_b, const int* plan,
+static int launch_moe_products(int mode, const void* x, const void* w_a, const void* w_b, const int* plan,
                                const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
                                void* out_t, float* out_f, size_t expert_stride, cudaStream_t s) {
   const int tile_rows = moe_tile_rows(rows, top, experts);
@@ -476,19 +488,23 @@ static int launch_moe_products(bool gated, const void* x, const void* w_a, const
   if (sizeof(T) == 2 && n_in % 8 == 0 && (((uintptr_t)x | (uintptr_t)w_a | (uintptr_t)w_b) & 15) == 0) {
     // bfloat16 rows on 16-byte boundaries: whole tiles, operands by asynchronous copies
     grid.z = 1;
-#define MOE_ASYNC_LAUNCH(GATED, ROWS, STAGES)                                                                          \
+#define MOE_ASYNC_LAUNCH(MODE, ROWS, STAGES)                                                                           \
   do {                                                                                                                 \
-    const size_t smem = sizeof(TileAsyncSmem<(GATED) ? 2 : 1, ROWS, STAGES>);                                          \
-    SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<GATED, ROWS, STAGES>,                                  \
+    const size_t smem = sizeof(TileAsyncSmem<(MODE) == MOE_GATED ? 2 : 1, ROWS, STAGES>);                              \
+    SRB_CUDA_CALL(cudaFuncSetAttribute(moe_product_async_kernel<MODE, ROWS, STAGES>,                                   \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                       \
-    SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<GATED, ROWS, STAGES>, grid, dim3(256), smem, s,                  \
+    SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<MODE, ROWS, STAGES>, grid, dim3(256), smem, s,                   \
                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan,      \
                              slot_row, experts, n_in, n_out, activation, (__nv_bfloat16*)out_t, out_f, expert_stride)); \
   } while (0)
     if (tile_rows == MOE_FEW_ROWS) {
-      if (gated) MOE_ASYNC_LAUNCH(true, MOE_FEW_ROWS, MOE_FEW_STAGES); else MOE_ASYNC_LAUNCH(false, MOE_FEW_ROWS, MOE_FEW_STAGES);
+      if (mode == MOE_GATED) MOE_ASYNC_LAUNCH(MOE_GATED, MOE_FEW_ROWS, MOE_FEW_STAGES);
+      else if (mode == MOE_ACT) MOE_ASYNC_LAUNCH(MOE_ACT, MOE_FEW_ROWS, MOE_FEW_STAGES);
+      else MOE_ASYNC_LAUNCH(MOE_DOWN, MOE_FEW_ROWS, MOE_FEW_STAGES);
     } else {
-      if (gated) MOE_ASYNC_LAUNCH(true, MOE_ROWS, TA_STAGES); else MOE_ASYNC_LAUNCH(false, MOE_ROWS, TA_STAGES);
+      if (mode == MOE_GATED) MOE_ASYNC_LAUNCH(MOE_GATED, MOE_ROWS, TA_STAGES);
+      else if (mode == MOE_ACT) MOE_ASYNC_LAUNCH(MOE_ACT, MOE_ROWS, TA_STAGES);
+      else MOE_ASYNC_LAUNCH(MOE_DOWN, MOE_ROWS, TA_STAGES);
     }
 #undef MOE_ASYNC_LAUNCH
     SRB_LAUNCH_CHECK("moe product");
@@ -496,23 +512,24 @@ static int launch_moe_products(bool gated, const void* x, const void* w_a, const
   }
   if (sizeof(T) == 2) {
     // bfloat16: the tensor cores
-    if (gated)
-      SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
-                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride));
-    else
-      SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
-                               (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,
-                               activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride));
+#define MOE_MMA_LAUNCH(MODE)                                                                                             \
+  SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<MODE>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,                 \
+                           (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,   \
+                           activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride))
+    if (mode == MOE_GATED) MOE_MMA_LAUNCH(MOE_GATED);
+    else if (mode == MOE_ACT) MOE_MMA_LAUNCH(MOE_ACT);
+    else MOE_MMA_LAUNCH(MOE_DOWN);
+#undef MOE_MMA_LAUNCH
     SRB_LAUNCH_CHECK("moe product");
     return SRB_OK;
   }
-  if (gated)
-    SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, true>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride));
-  else
-    SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, false>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b,
-                             plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride));
+#define MOE_PLAIN_LAUNCH(MODE)                                                                                           \
+  SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, MODE>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b, \
+                           plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride))
+  if (mode == MOE_GATED) MOE_PLAIN_LAUNCH(MOE_GATED);
+  else if (mode == MOE_ACT) MOE_PLAIN_LAUNCH(MOE_ACT);
+  else MOE_PLAIN_LAUNCH(MOE_DOWN);
+#undef MOE_PLAIN_LAUNCH
   SRB_LAUNCH_CHECK("moe product");
   return SRB_OK;
 }
@@ -527,10 +544,25 @@ extern "C" int srb_moe_gated_up(const void* h, const void* w_gate, const void* w
   if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_gated_up: unknown activation %d", activation);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
+    return launch_moe_products<float>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(true, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
+    return launch_moe_products<__nv_bfloat16>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
   SRB_FAIL("moe_gated_up: unknown dtype %d", dtype);
+}
+
+// The first product of experts without a gate: act[slot, :] = activation(W_up[e] h[row]); w_up: [experts, inner, width].
+extern "C" int srb_moe_act_up(const void* h, const void* w_up, const int* plan, const int* slot_row, int rows, int top,
+                              int experts, int width, int inner, int activation, void* act, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0 || inner <= 0) SRB_FAIL("moe_act_up: sizes %d, %d must be positive", width, inner);
+  if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_act_up: unknown activation %d", activation);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t stride = (size_t)inner * width;
+  if (dtype == SRB_DTYPE_F32)
+    return launch_moe_products<float>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, stride, s);
+  if (dtype == SRB_DTYPE_BF16)
+    return launch_moe_products<__nv_bfloat16>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, stride, s);
+  SRB_FAIL("moe_act_up: unknown dtype %d", dtype);
 }
 
 // act: [rows * top, inner]; w_down: [experts, width, inner]; y: float [rows * top, width]
@@ -540,19 +572,22 @@ extern "C" int srb_moe_down(const void* act, const void* w_down, const int* plan
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_down: sizes %d, %d must be positive", width, inner);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
+    return launch_moe_products<float>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(false, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
+    return launch_moe_products<__nv_bfloat16>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
   SRB_FAIL("moe_down: unknown dtype %d", dtype);
 }
 
+// `base` (float [rows, width], or null): a term that every row gets beside its experts' (an expert that all rows share);
+// it is the first term of the sum.
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ entry_slot,
-                                   const float* __restrict__ weights, int top, int width, float* __restrict__ out) {
+                                   const float* __restrict__ weights, int top, int width, float* __restrict__ out,
+                                   const float* __restrict__ base) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float sum = 0.f;
+    float sum = base ? base[(size_t)row * width + i] : 0.f;
     for (int k = 0; k < top; ++k) {
       const int slot = entry_slot[(size_t)row * top + k];
       if (slot >= 0) sum += weights[(size_t)row * top + k] * y[(size_t)slot * width + i];
@@ -561,13 +596,18 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   }
 }
 
-extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
-                               float* out, void* stream) {
+extern "C" int srb_moe_combine_onto(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
+                                    float* out, const float* base, void* stream) {
   if (rows <= 0) return SRB_OK;
   SRB_CUDA_CALL(srb_launch(moe_combine_kernel, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, y,
-                           entry_slot, weights, top, width, out));
+                           entry_slot, weights, top, width, out, base));
   SRB_LAUNCH_CHECK("moe_combine");
   return SRB_OK;
+}
+
+extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
+                               float* out, void* stream) {
+  return srb_moe_combine_onto(y, entry_slot, weights, rows, top, width, out, nullptr, stream);
 }
 
 // rows of h in slot order: out[slot, :] = h[slot_row[slot], :] (16 bytes a thread where the rows allow it), for

@@ -46,7 +46,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        float eps, const float* __restrict__ inv_freq,
                                        const float* __restrict__ angles, int rotary_dim,
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
-                                       int num_pages, int heads_to_do, int vector_ok, int rounds, int* error_word) {
+                                       int num_pages, int heads_to_do, int vector_ok, int rounds, int* error_word,
+                                       float magnitude, int values_from_keys) {
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
   // The table of angles needs only the step's index arrays and constants: it is computed before
   // the wait for the kernel ahead (whose product this kernel reads) and overlaps that kernel's end.
@@ -66,6 +67,12 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
     const float pos = (float)positions[row];
     for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) sincosf(pos * inv_freq[i], &sin_table[i], &cos_table[i]);
   }
+  if (rotate && magnitude != 1.0f) {       // each thread scales the entries it wrote itself
+    for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) {
+      sin_table[i] = __fmul_rn(sin_table[i], magnitude);
+      cos_table[i] = __fmul_rn(cos_table[i], magnitude);
+    }
+  }
   srb_grid_dependency_wait();
   srb_mark(SRB_MARK_ROPE, 1);
   __syncthreads();
@@ -73,7 +80,9 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   for (int round = 0; round < rounds; ++round) {
   const int head = (blockIdx.y * rounds + round) * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
   if (head >= heads_to_do) break;
-  const size_t src_offset = (size_t)row * qkv_stride + (size_t)head * head_dim;
+  // with values_from_keys the projection holds q and k heads only: a v head is its k head as projected, unrotated
+  const size_t src_offset = (size_t)row * qkv_stride +
+                            (size_t)(values_from_keys && head >= n_q + n_kv ? head - n_kv : head) * head_dim;
 
   const bool is_q = head < n_q;
   const bool is_k = !is_q && head < n_q + n_kv;
@@ -361,7 +370,7 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                            const float* __restrict__ inv_freq, const float* __restrict__ angles,
                            const float* __restrict__ cos_sin, int rows, int n_q, int n_kv, int page_size, int num_pages,
-                           int* error_word) {
+                           int* error_word, float magnitude, int values_from_keys) {
   // cos_sin: the rows' cosines and sines [rows, 128] (64 cosines, then 64 sines) computed once for the step by
   // rope_table_kernel, or null: then this block computes its rows' own, with the same arithmetic
   constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_THREADS / 8, STAGES = ROW_STAGES;
@@ -374,8 +383,10 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
   norm_weights[1][threadIdx.x] = k_norm ? k_norm[threadIdx.x] : 1.f;
   const int group = threadIdx.x >> 3, l = threadIdx.x & 7;     // this thread's head of a pass, its place in the head
   const bool rotate = inv_freq || angles;
-  const int heads_stored = slots ? n_q + 2 * n_kv : n_q;       // heads of a row that are brought in
-  const size_t stage_bytes = (size_t)heads_stored * D * sizeof(T);
+  const int heads_stored = slots ? n_q + 2 * n_kv : n_q;       // heads of a row that are worked on
+  // ... and those that are brought in: with values_from_keys a v head is read from its k head's place
+  const int heads_loaded = slots ? n_q + (values_from_keys ? 1 : 2) * n_kv : n_q;
+  const size_t stage_bytes = (size_t)heads_loaded * D * sizeof(T);
   const int row_chunks = (int)(stage_bytes / 16);              // 16-byte pieces of a row
   const int pair0 = l * 8;                                     // the eight pairs this lane holds
   srb_grid_dependency_wait();
@@ -393,7 +404,10 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
             cp_async_16(&row_cos_sin[stage][threadIdx.x * 4], cos_sin + (size_t)row * D + threadIdx.x * 4, 16);
         } else if (threadIdx.x < HALF) {
           const float angle = angles ? angles[(size_t)row * HALF + threadIdx.x] : (float)positions[row] * inv_freq[threadIdx.x];
-          sincosf(angle, &row_cos_sin[stage][HALF + threadIdx.x], &row_cos_sin[stage][threadIdx.x]);
+          float sn, cs;
+          sincosf(angle, &sn, &cs);
+          row_cos_sin[stage][HALF + threadIdx.x] = magnitude != 1.0f ? __fmul_rn(sn, magnitude) : sn;
+          row_cos_sin[stage][threadIdx.x] = magnitude != 1.0f ? __fmul_rn(cs, magnitude) : cs;
         }
       }
       if (threadIdx.x == ROW_THREADS - 1) {
@@ -439,7 +453,8 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
       // values and stores nothing.
       const bool live = head < heads;
       const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
-      const Raw16<T> raw = load_raw16(src + (size_t)min(head, heads - 1) * D);
+      const int from = min(head, heads - 1);
+      const Raw16<T> raw = load_raw16(src + (size_t)(values_from_keys && from >= n_q + n_kv ? from - n_kv : from) * D);
       if (live && !is_q && !is_k) {                            // a v head: no arithmetic
         store_raw16(v_pool + kv_base + (size_t)(head - n_q - n_kv) * kv_step, raw);
       }
@@ -466,25 +481,36 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
 // The cosines and sines of every row's angles, once for a step: out[r, 0..half) = cos, out[r, half..2 half) = sin
 // of float(positions[r]) * inv_freq[i] (or of angles[r, i]), the arithmetic of the kernels above.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  const float* __restrict__ angles, int rows, int half, float* __restrict__ out) {
+                                  const float* __restrict__ angles, int rows, int half, float* __restrict__ out,
+                                  float magnitude) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * half) return;
   const int row = i / half, pair = i - row * half;
   float sn, cs;
   sincosf(angles ? angles[i] : (float)positions[row] * inv_freq[pair], &sn, &cs);
+  if (magnitude != 1.0f) {
+    sn = __fmul_rn(sn, magnitude);
+    cs = __fmul_rn(cs, magnitude);
+  }
   out[(size_t)row * 2 * half + pair] = cs;
   out[(size_t)row * 2 * half + half + pair] = sn;
 }
 
-extern "C" int srb_rope_table(const int* positions, const float* inv_freq, const float* angles, int rows, int rotary_dim,
-                              float* out, void* stream) {
+// `magnitude` multiplies every cosine and sine (1 leaves them as they are).
+extern "C" int srb_rope_table_scaled(const int* positions, const float* inv_freq, const float* angles, int rows, int rotary_dim,
+                                     float* out, float magnitude, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (rotary_dim <= 0 || (rotary_dim & 1) || (!inv_freq && !angles) || !out)
     SRB_FAIL("rope_table: an even rotary width, frequencies or angles, and an output are needed");
   const int total = rows * (rotary_dim >> 1);
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, angles, rows, rotary_dim >> 1, out);
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, angles, rows, rotary_dim >> 1, out, magnitude);
   SRB_LAUNCH_CHECK("rope_table");
   return SRB_OK;
+}
+
+extern "C" int srb_rope_table(const int* positions, const float* inv_freq, const float* angles, int rows, int rotary_dim,
+                              float* out, void* stream) {
+  return srb_rope_table_scaled(positions, inv_freq, angles, rows, rotary_dim, out, 1.0f, stream);
 }
 
 // How many rows a step must have for the kernel that can take the table of srb_rope_table (fewer rows compute
@@ -514,12 +540,35 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
 
 // The same with `cos_sin`: the table of srb_rope_table for these rows (float [rows, rotary_dim], 16-byte aligned),
 // or null.  Only the kernel for many rows reads it; the values are those the kernels compute themselves.
+extern "C" int srb_qk_norm_rope_kv_ex(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                      int qkv_stride, void* q_out, void* k_pool, void* v_pool, const int* positions,
+                                      const int* slots, const float* q_norm, const float* k_norm, float eps,
+                                      const float* inv_freq, const float* angles, const float* cos_sin, int rotary_dim,
+                                      int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
+                                      int num_pages, int* error_word, int dtype, float magnitude, int values_from_keys,
+                                      void* stream);
+
 extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
                                          int qkv_stride, void* q_out, void* k_pool, void* v_pool, const int* positions,
                                          const int* slots, const float* q_norm, const float* k_norm, float eps,
                                          const float* inv_freq, const float* angles, const float* cos_sin, int rotary_dim,
                                          int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
                                          int num_pages, int* error_word, int dtype, void* stream) {
+  return srb_qk_norm_rope_kv_ex(qkv, qkv_parts, num_parts, part_stride, qkv_stride, q_out, k_pool, v_pool, positions, slots,
+                                q_norm, k_norm, eps, inv_freq, angles, cos_sin, rotary_dim, interleaved, rows, n_q, n_kv,
+                                head_dim, page_size, num_pages, error_word, dtype, 1.0f, 0, stream);
+}
+
+// The same with two more terms.  `magnitude` multiplies the cosines and sines of the rotation (a table in `cos_sin`
+// must hold them multiplied already: srb_rope_table_scaled).  `values_from_keys`: the projection holds q and k heads
+// only, and the value stored for a key is the key as projected: before its norm, if it has one, and before the rotation.
+extern "C" int srb_qk_norm_rope_kv_ex(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                      int qkv_stride, void* q_out, void* k_pool, void* v_pool, const int* positions,
+                                      const int* slots, const float* q_norm, const float* k_norm, float eps,
+                                      const float* inv_freq, const float* angles, const float* cos_sin, int rotary_dim,
+                                      int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
+                                      int num_pages, int* error_word, int dtype, float magnitude, int values_from_keys,
+                                      void* stream) {
   if (rows <= 0) return SRB_OK;
   if (n_q <= 0 || n_kv <= 0 || head_dim <= 0 || page_size <= 0)
     SRB_FAIL("qk_norm_rope_kv: head counts, head_dim and page size must be positive");
@@ -538,7 +587,8 @@ extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
   // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
   const int row_bytes_ok = dtype == SRB_DTYPE_F32 || qkv_stride % 8 == 0;      // 16-byte accesses of eight values
-  const size_t staged = (size_t)ROW_STAGES * heads * 128 * (dtype == SRB_DTYPE_F32 ? 4 : 2);     // the ring of rows
+  const int heads_loaded = slots ? n_q + (values_from_keys ? 1 : 2) * n_kv : n_q;
+  const size_t staged = (size_t)ROW_STAGES * heads_loaded * 128 * (dtype == SRB_DTYPE_F32 ? 4 : 2);     // the ring of rows
   if (rows >= srb_rope_table_min_rows() && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok &&
       staged <= 200 * 1024) {
     const float* table = (cos_sin && (((uintptr_t)cos_sin) & 15) == 0) ? cos_sin : nullptr;
@@ -553,14 +603,14 @@ extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(blocks), dim3(ROW_THREADS), staged, s,
                                (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions,
                                slots, q_norm, k_norm, eps, inv_freq, angles, table, rows, n_q, n_kv, page_size, num_pages,
-                               error_word));
+                               error_word, magnitude, values_from_keys));
     } else if (dtype == SRB_DTYPE_BF16) {
       SRB_CUDA_CALL(cudaFuncSetAttribute(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)staged));
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(blocks), dim3(ROW_THREADS), staged, s,
                                (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                                (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, table, rows, n_q,
-                               n_kv, page_size, num_pages, error_word));
+                               n_kv, page_size, num_pages, error_word, magnitude, values_from_keys));
     } else {
       SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
     }
@@ -576,13 +626,14 @@ extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<float>, grid, dim3(ROPE_WARPS * 32), smem, s, (const float*)qkv,
                              qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool,
                              (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, rotary_dim,
-                             interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, rounds, error_word));
+                             interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, rounds, error_word,
+                             magnitude, values_from_keys));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<__nv_bfloat16>, grid, dim3(ROPE_WARPS * 32), smem, s,
                              (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
                              (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
                              q_norm, k_norm, eps, inv_freq, angles, rotary_dim, interleaved, n_q, n_kv, head_dim,
-                             page_size, num_pages, heads, vector_ok, rounds, error_word));
+                             page_size, num_pages, heads, vector_ok, rounds, error_word, magnitude, values_from_keys));
   else
     SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");

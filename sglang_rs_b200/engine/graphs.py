@@ -186,7 +186,7 @@ class DecodeGraphs:
 
     def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits) -> None:
         ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits)
-        caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+        caches = list(self.cache.layer_caches)      # one per program call, then the embedding's if it keeps state
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(current)

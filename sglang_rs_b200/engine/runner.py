@@ -311,7 +311,7 @@ class ModelRunner:
                 captured = True
             else:
                 ctx, logit_rows = self.planner.flatten(entries, token_source)
-                caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+                caches = list(self.cache.layer_caches)      # one per program call, then the embedding's if it keeps state
                 with ops.stream_scope():
                     logits = self.model.forward(ctx, caches, logit_rows)
         except Exception:

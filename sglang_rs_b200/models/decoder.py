@@ -8,6 +8,9 @@ of an earlier call instead of keeping one (it then writes nothing).  A call may 
 part of ``pass_entries`` that runs right before it: the head of a pass over a stretch of
 layers that the program walks several times (``parts/loop.py``); it is handed the stream,
 the embedding output and the number of the pass, and returns the new stream.
+
+An embedding may keep state per request too (the token before, for a table indexed by pairs of tokens): its need
+is the entry after the calls' in ``cache_needs()``, and ``forward`` hands it the cache at that index.
 """
 from __future__ import annotations
 
@@ -76,8 +79,10 @@ class DecoderModel(Part):
 
     def cache_needs(self) -> List[CacheNeed]:
         """One entry per program call; a call that reads another's cache needs none."""
-        return [None if call.cache_from is not None else self.layers[call.layer].cache_need()
-                for call in self.program]
+        needs = [None if call.cache_from is not None else self.layers[call.layer].cache_need()
+                 for call in self.program]
+        extra = self.embedding.cache_need() if hasattr(self.embedding, "cache_need") else None
+        return needs + [extra] if extra is not None else needs
 
     def forward(self, ctx, caches: Sequence, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Runs the rows of ``ctx``; returns 32-bit logits of the rows in ``logit_rows``
@@ -85,7 +90,10 @@ class DecoderModel(Part):
         if self.native is not None and trace.active is None and all(
                 cache is not None and hasattr(cache, "k_pool") for cache in caches):
             return self.native.run(ctx, caches, logit_rows)
-        residual = self.embedding.forward(ctx, ctx.token_ids)
+        if len(caches) > len(self.program):
+            residual = self.embedding.forward(ctx, ctx.token_ids, caches[len(self.program)])
+        else:
+            residual = self.embedding.forward(ctx, ctx.token_ids)
         delta = None
         origin = None
         if any(call.entry is not None for call in self.program):

@@ -268,7 +268,7 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
 
 
 #: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
 
 
 def activation_code(name: str) -> int:
@@ -308,7 +308,8 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                     inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, n_q: int, n_kv: int,
                     head_dim: int, error_word: torch.Tensor, angles: Optional[torch.Tensor] = None,
-                    cos_sin: Optional[torch.Tensor] = None) -> None:
+                    cos_sin: Optional[torch.Tensor] = None, magnitude: float = 1.0,
+                    values_from_keys: bool = False) -> None:
     """Per-head norm of q and k, rotation of q and k, q to ``q_out``, k and v into the pages.
 
     ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order,
@@ -317,7 +318,9 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
     With ``slots`` None nothing is written to the pages.  The rotation takes its angles as
     ``positions[r] * inv_freq[i]`` or, if ``angles`` (float32 [rows, rotary_dim / 2]) is given,
     from there.  ``cos_sin``: the table of :func:`rope_table` for these rows; the kernel for many rows
-    then reads the cosines and sines instead of computing them (the same values)."""
+    then reads the cosines and sines instead of computing them (the same values).  ``magnitude`` multiplies the
+    cosines and sines (a ``cos_sin`` table must hold them multiplied already).  With ``values_from_keys`` the rows
+    of ``qkv`` hold q and k heads only, and the value stored for a key is the key as projected, unrotated."""
     _need(qkv, "qkv"); _need(q_out, "q_out"); _need(positions, "positions", torch.int32)
     if angles is not None:
         _need(angles, "angles", torch.float32)
@@ -338,8 +341,8 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
         num_pages, pool_heads, page_size, pool_dim = k_pool.shape
         if (pool_heads, pool_dim) != (n_kv, head_dim) or v_pool.shape != k_pool.shape:
             raise KernelError("qk_norm_rope_kv: pools must be [pages, n_kv, page_size, head_dim]")
-        if qkv.shape[-1] < (n_q + 2 * n_kv) * head_dim:
-            raise KernelError("qk_norm_rope_kv: qkv is narrower than q, k and v together")
+        if qkv.shape[-1] < (n_q + (1 if values_from_keys else 2) * n_kv) * head_dim:
+            raise KernelError("qk_norm_rope_kv: qkv is narrower than its heads together")
     for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
         if w is not None:
             _need(w, name, torch.float32)
@@ -354,23 +357,24 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
         if cos_sin.shape != (rows, rotary_dim):
             raise KernelError("qk_norm_rope_kv: cos_sin must be [rows, rotary_dim]")
     lib = load_library("rope_kv")
-    _check(lib, lib.srb_qk_norm_rope_kv_table(
+    _check(lib, lib.srb_qk_norm_rope_kv_ex(
         _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), qkv.stride(-2), _ptr(q_out), _ptr(k_pool),
         _ptr(v_pool), _ptr(positions), _ptr(slots), _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq),
         _ptr(angles), _ptr(cos_sin), rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages,
-        _ptr(error_word), dtype_code(q_out.dtype), _stream()))
+        _ptr(error_word), dtype_code(q_out.dtype), ctypes.c_float(magnitude), int(values_from_keys), _stream()))
 
 
 @traced("rope_kv")
 def rope_table(positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
-               angles: Optional[torch.Tensor] = None) -> torch.Tensor:
+               angles: Optional[torch.Tensor] = None, magnitude: float = 1.0) -> torch.Tensor:
     """float32 [rows, rotary_dim]: per row the cosines, then the sines, of ``positions[r] * inv_freq[i]`` (or of
     ``angles[r, i]``), computed once for a step; the step executor hands it to the rope kernel of every layer."""
     _need(positions, "positions", torch.int32)
     rows = positions.numel()
     out = torch.empty((rows, rotary_dim), dtype=torch.float32, device=positions.device)
     lib = load_library("rope_kv")
-    _check(lib, lib.srb_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(angles), rows, rotary_dim, _ptr(out), _stream()))
+    _check(lib, lib.srb_rope_table_scaled(_ptr(positions), _ptr(inv_freq), _ptr(angles), rows, rotary_dim, _ptr(out),
+                                          ctypes.c_float(magnitude), _stream()))
     return out
 
 
@@ -384,8 +388,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
                     scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
-                    error_word: torch.Tensor, sinks: Optional[torch.Tensor] = None) -> None:
+                    error_word: torch.Tensor, sinks: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
+
+    A row at position p sees the keys max(0, p - window + 1) .. p (``window`` 0: from 0) and, with ``chunk`` > 0,
+    of those only the keys of its own chunk of positions, floor(p / chunk) * chunk .. p.
 
     ``sinks`` (float32, one per query head): the softmax's denominator also holds exp(sink_h), a term without
     key or value.  ``v_pool`` may hold rows narrower than the keys (``out`` is as wide as they are), and may be
@@ -417,10 +424,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
     lib = load_library("attention")
-    _check(lib, lib.srb_paged_attention_ex(
+    _check(lib, lib.srb_paged_attention_masked(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
         _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
-        num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
+        num_pages, int(window), int(chunk), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
         dtype_code(q.dtype), _ptr(sinks), value_dim, _stream()), launches=2 if split_size else 1)
 
 
@@ -510,8 +517,10 @@ def decode_splits_bound(max_keys: int) -> int:
 def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                      positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                      scale: float, window: int, scratch_acc: torch.Tensor, scratch_ml: torch.Tensor,
-                     counters: torch.Tensor, error_word: torch.Tensor, max_keys: Optional[int] = None) -> None:
-    """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128.
+                     counters: torch.Tensor, error_word: torch.Tensor, max_keys: Optional[int] = None,
+                     chunk: int = 0) -> None:
+    """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128; ``window`` and ``chunk`` as in
+    :func:`paged_attention`.
 
     The keys of a (row, kv head) are shared by ``decode_splits(rows, n_kv, max_keys)`` blocks
     (``max_keys``: the most keys any row sees, if known); the block that finishes last merges them.  ``counters``: int32, zero, at least rows * n_kv entries; they
@@ -534,10 +543,10 @@ def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     if counters.numel() < rows * n_kv:
         raise KernelError("decode_attention: too few counters")
     lib = load_library("attention_decode")
-    _check(lib, lib.srb_decode_attention(
+    _check(lib, lib.srb_decode_attention_masked(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(counters),
         _ptr(positions), _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim,
-        page_size, num_pages, int(window), splits, ctypes.c_float(scale), _ptr(error_word), _stream()))
+        page_size, num_pages, int(window), int(chunk), splits, ctypes.c_float(scale), _ptr(error_word), _stream()))
 
 
 def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
@@ -550,7 +559,7 @@ def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int
 @traced("attention_prefill")
 def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                     tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
-                    error_word: torch.Tensor) -> None:
+                    error_word: torch.Tensor, chunk: int = 0) -> None:
     """Attention of prompt portions, bfloat16.  ``tiles`` is int32 [n, 4]: first row of the
     step, rows (at most 64, consecutive rows of one request), request index, first position.
     Rows outside the tiles are left untouched."""
@@ -562,9 +571,9 @@ def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
         raise KernelError("tiled_attention: shapes of q, out, the pools and the tiles do not agree")
     lib = load_library("attention_prefill")
-    _check(lib, lib.srb_prefill_attention(
+    _check(lib, lib.srb_prefill_attention_masked(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], _ptr(block_table),
-        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), ctypes.c_float(scale),
+        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), int(chunk), ctypes.c_float(scale),
         _ptr(error_word), _stream()))
 
 
@@ -581,7 +590,7 @@ def tiled_attention_tc_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: 
 @traced("attention_prefill")
 def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                        tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
-                       error_word: torch.Tensor) -> None:
+                       error_word: torch.Tensor, chunk: int = 0) -> None:
     """Attention of prompt portions on tcgen05 tensor cores (S, P and O in tensor memory, operands
     by TMA).  ``tiles`` as for :func:`tiled_attention`, with at most 128 rows per tile."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
@@ -592,9 +601,9 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
         raise KernelError("tiled_attention_tc: shapes of q, out, the pools and the tiles do not agree")
     lib = load_library("attention_prefill_tc")
-    _check(lib, lib.srb_prefill_attention_tc(
+    _check(lib, lib.srb_prefill_attention_tc_masked(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], rows, _ptr(block_table),
-        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), ctypes.c_float(scale),
+        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), int(chunk), ctypes.c_float(scale),
         _ptr(error_word), _stream()))
 
 
@@ -692,8 +701,14 @@ GROUPED_TILE_SLOTS = int(os.environ.get("SRB_GROUPED_TILE_SLOTS", "256"))
 
 @traced("routed_experts")
 def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
-                   activation: str, renormalize: bool, error_word: torch.Tensor) -> torch.Tensor:
+                   activation: str, renormalize: bool, error_word: torch.Tensor, *, gated: bool = True,
+                   router_bias: Optional[torch.Tensor] = None, base: Optional[torch.Tensor] = None) -> torch.Tensor:
     """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].
+
+    ``gated`` False: an expert is W_down act(W_up h) and ``w_gate_up`` holds the up matrices alone
+    [experts, inner, width].  ``router_bias`` (float32 [experts]) is added to the router's logits before the choice.
+    ``base`` (float32 [rows, width]): a term that every row gets beside its experts' (an expert that all rows
+    share); the sum starts from it.
 
     ``router`` [experts, width]; ``w_gate_up`` [experts, 2 * inner, width] (an expert's gate rows over its up rows);
     ``w_down`` [experts, width, inner], all of h's dtype.  Scores are a softmax over all experts, in 32-bit; with
@@ -706,10 +721,18 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     128 consecutive rows that TMA can fetch."""
     _need(h, "h"); _need(router, "router", h.dtype); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
     rows, width = h.shape
-    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
-    if (router.shape != (experts, width) or w_gate_up.shape != (experts, 2 * inner, width)
+    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // (2 if gated else 1)
+    if (router.shape != (experts, width) or w_gate_up.shape != (experts, (2 if gated else 1) * inner, width)
             or w_down.shape != (experts, width, inner)):
         raise KernelError("routed_experts: shapes of the router and the experts do not agree")
+    if router_bias is not None:
+        _need(router_bias, "router_bias", torch.float32)
+        if router_bias.numel() != experts:
+            raise KernelError("routed_experts: one router bias per expert is needed")
+    if base is not None:
+        _need(base, "base", torch.float32)
+        if base.shape != (rows, width):
+            raise KernelError("routed_experts: the shared term must be float32 [rows, width]")
     lib = load_library("moe")
     device = h.device
     entries = rows * top
@@ -725,9 +748,9 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     y = torch.empty((entries, width), dtype=torch.float32, device=device)
     out = torch.empty((rows, width), dtype=torch.float32, device=device)
     code, stream = dtype_code(h.dtype), _stream()
-    if rows >= ROUTER_PRODUCT_MIN_ROWS:
+    if rows >= ROUTER_PRODUCT_MIN_ROWS or router_bias is not None:
         # many rows: the logits are a product like any other (32-bit accumulation, 32-bit result), the choice a kernel of its own
-        logits = linear(h, router, out_dtype=torch.float32, error_word=error_word)
+        logits = linear(h, router, router_bias, out_dtype=torch.float32, error_word=error_word)
         _check(lib, lib.srb_moe_select(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, experts, top, int(renormalize),
                                        _ptr(chosen), _ptr(weights), stream))
     else:
@@ -741,20 +764,26 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
         gathered = torch.empty((entries, width), dtype=h.dtype, device=device)
         _check(lib, lib.srb_moe_gather(_ptr(h), _ptr(slot_row), entries, width, _ptr(gathered), code, stream))
         _check(product, product.srb_gemm_bf16_grouped(
-            _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, tile_slots, entries, experts, 2 * inner, inner, width,
-            inner, inner, GEMM_MODES["gated"], activation_code(activation), _ptr(error_word), stream))
+            _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, tile_slots, entries, experts,
+            (2 if gated else 1) * inner, inner, width, inner, inner if gated else 0, GEMM_MODES["gated" if gated else "act"],
+            activation_code(activation), _ptr(error_word), stream))
         _check(product, product.srb_gemm_bf16_grouped(
             _ptr(act), _ptr(w_down), _ptr(y), _ptr(plan), max_tiles, tile_slots, entries, experts, width, width, inner, width, 0,
             GEMM_MODES["f32"], 0, _ptr(error_word), stream))
     else:
         element = h.element_size()
-        w_up = ctypes.c_void_p(w_gate_up.data_ptr() + inner * width * element)
-        _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate_up), w_up, ctypes.c_longlong(2 * inner * width), _ptr(plan),
-                                         _ptr(slot_row), rows, top, experts, width, inner, activation_code(activation),
-                                         _ptr(act), code, stream))
+        if gated:
+            w_up = ctypes.c_void_p(w_gate_up.data_ptr() + inner * width * element)
+            _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate_up), w_up, ctypes.c_longlong(2 * inner * width), _ptr(plan),
+                                             _ptr(slot_row), rows, top, experts, width, inner, activation_code(activation),
+                                             _ptr(act), code, stream))
+        else:
+            _check(lib, lib.srb_moe_act_up(_ptr(h), _ptr(w_gate_up), _ptr(plan), _ptr(slot_row), rows, top, experts, width,
+                                           inner, activation_code(activation), _ptr(act), code, stream))
         _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
                                      stream))
-    _check(lib, lib.srb_moe_combine(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), stream))
+    _check(lib, lib.srb_moe_combine_onto(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), _ptr(base),
+                                         stream))
     return out
 
 
@@ -874,7 +903,7 @@ def gated_product(x: torch.Tensor, weight: torch.Tensor, inner: int, error_word:
     return act
 
 
-GEMM_MODES = {"bf16": 0, "f32": 1, "gated": 2, "partial": 3, "add": 4}
+GEMM_MODES = {"bf16": 0, "f32": 1, "gated": 2, "partial": 3, "add": 4, "act": 5}
 #: the blocks of a thread-block cluster: at most this many K splits add their sums inside the kernel
 GEMM_CLUSTER_SPLITS = 8
 
@@ -888,7 +917,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mod
     x [tokens, k], w [rows, k], k a multiple of 8.  ``mode``: ``bf16`` / ``f32`` store
     [tokens, features]; ``gated`` treats w as gate rows [0, features) stacked over up rows
     [up_row_offset, up_row_offset + features) and stores act(gate) * up (``activation``: a name of
-    ``ACTIVATIONS``); ``partial`` stores
+    ``ACTIVATIONS``); ``act`` stores act(x w^T) in bfloat16; ``partial`` stores
     ``splits`` float partial sums [splits, tokens, features] that the consumer adds in order;
     ``add`` adds the product to ``out`` (float32 [tokens, features], e.g. the residual stream) in
     place, K cut into at most ``GEMM_CLUSTER_SPLITS`` blocks that sum inside the kernel in block order.
@@ -952,6 +981,184 @@ def pair_gemm_takes(tokens: int, features: int, k: int) -> bool:
 def gemm_bf16_takes(k: int) -> bool:
     """TMA needs 16-byte rows: the inner size must be a multiple of 8 bfloat16 values."""
     return k % 8 == 0
+
+
+@traced("gemm")
+def activated_product(x: torch.Tensor, weight: torch.Tensor, activation: str,
+                      error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(x weight^T): the first product of a feed-forward without a gate.  bfloat16 with few rows: the tcgen05
+    kernel applies the activation in its epilogue; otherwise the product followed by the activation kernel."""
+    if (x.dtype == torch.bfloat16 and x.shape[0] <= OWN_GEMM_MAX_TOKENS and error_word is not None
+            and gemm_bf16_takes(x.shape[1])):
+        return gemm_bf16(x, weight, error_word, mode="act", activation=activation)
+    up = linear(x, weight, error_word=error_word)
+    activate(up, up, activation)
+    return up
+
+
+@traced("activation")
+def activate(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(x), element by element (``out`` may be ``x``)."""
+    _need(x, "x"); _need(out, "out", x.dtype)
+    if out.shape != x.shape:
+        raise KernelError("activate: x and out differ in shape")
+    lib = load_library("streams")
+    _check(lib, lib.srb_activate(_ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), activation_code(activation),
+                                 dtype_code(x.dtype), _stream()))
+
+
+@traced("activation")
+def softcap(values: torch.Tensor, cap: float) -> None:
+    """values <- cap * tanh(values / cap), in place (float32)."""
+    _need(values, "values", torch.float32)
+    lib = load_library("streams")
+    _check(lib, lib.srb_softcap(_ptr(values), ctypes.c_longlong(values.numel()), ctypes.c_float(cap), _stream()))
+
+
+# --------------------------------------------------------------------------- copies of the residual stream
+
+@traced("embedding")
+def embedding_pairs(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, error_word: torch.Tensor, *,
+                    scale: float = 1.0, copies: int = 1, pairs: Optional[torch.Tensor] = None, buckets: int = 0,
+                    mul_prev: int = 0, mul_cur: int = 0, positions: Optional[torch.Tensor] = None,
+                    row_request: Optional[torch.Tensor] = None, cu_rows: Optional[torch.Tensor] = None,
+                    state_slots: Optional[torch.Tensor] = None, last_token: Optional[torch.Tensor] = None) -> None:
+    """out[r, c, :] = table[ids[r]] * scale + pairs[row(r)] for every copy c; float32 [rows, copies, width].
+
+    ``pairs`` [buckets + 1, width]: row(r) = (previous token * mul_prev + ids[r] * mul_cur) mod buckets, and row
+    ``buckets`` where ``positions[r]`` is 0.  The previous token of a request's first row in this step is
+    ``last_token[state_slots[request]]``; :func:`remember_tokens` stores it after the step's embedding."""
+    _need(ids, "ids", torch.int32); _need(table, "table"); _need(out, "out", torch.float32)
+    rows, width = ids.numel(), table.shape[1]
+    if out.numel() != rows * copies * width:
+        raise KernelError("embedding_pairs: out must hold rows * copies * width floats")
+    if pairs is not None:
+        _need(pairs, "pairs", table.dtype)
+        if pairs.shape != (buckets + 1, width):
+            raise KernelError("embedding_pairs: the pair table must be [buckets + 1, width]")
+        for name, tensor in (("positions", positions), ("row_request", row_request), ("cu_rows", cu_rows),
+                             ("state_slots", state_slots), ("last_token", last_token)):
+            if tensor is None:
+                raise KernelError(f"embedding_pairs: {name} is needed with a pair table")
+            _need(tensor, name, torch.int32)
+    lib = load_library("streams")
+    _check(lib, lib.srb_embedding_pairs(
+        _ptr(ids), _ptr(positions), _ptr(row_request), _ptr(cu_rows), _ptr(state_slots), _ptr(last_token), _ptr(table),
+        _ptr(pairs), _ptr(out), rows, width, table.shape[0], int(copies), ctypes.c_longlong(buckets),
+        ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), ctypes.c_float(scale), _ptr(error_word),
+        dtype_code(table.dtype), _stream()))
+
+
+@traced("embedding")
+def remember_tokens(ids: torch.Tensor, cu_rows: torch.Tensor, state_slots: torch.Tensor, last_token: torch.Tensor,
+                    requests: int) -> None:
+    """last_token[state_slots[q]] = the last id that request q brought in this step."""
+    _need(ids, "ids", torch.int32); _need(cu_rows, "cu_rows", torch.int32); _need(state_slots, "state_slots", torch.int32)
+    _need(last_token, "last_token", torch.int32)
+    lib = load_library("streams")
+    _check(lib, lib.srb_remember_tokens(_ptr(ids), _ptr(cu_rows), _ptr(state_slots), _ptr(last_token), int(requests),
+                                        _stream()))
+
+
+@traced("norm")
+def stream_step(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor], spread: Optional[torch.Tensor],
+                gather: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                row_index: Optional[torch.Tensor] = None, norm: bool = True) -> None:
+    """One pass over the copies of the residual stream ``x`` (float32 [rows, streams, width]).
+
+    With ``mix`` ([streams, streams], indexed [from, to]) and ``spread`` ([streams]): every copy is replaced, all at
+    once from the old ones, x_t <- sum_s mix[s, t] x_s + spread[t] * y, where ``y`` is the result of the sublayer
+    before ([rows, width] of ``out``'s dtype or float32, or float32 [parts, rows, width] partial sums added in order).
+    With ``gather`` ([streams]): u = sum_t gather[t] x_t and ``out`` = u / sqrt(mean(u^2) + eps) * weight (``norm``
+    False: u * weight; ``weight`` None: no scaling).  With ``row_index`` only those rows are read, ``out[i]`` is
+    written, and the copies in memory stay as they are."""
+    _need(x, "x", torch.float32)
+    if x.dim() != 3:
+        raise KernelError("stream_step: x must be [rows, streams, width]")
+    total_rows, streams, width = x.shape
+    rows = total_rows if row_index is None else row_index.numel()
+    whole = parts = None
+    num_parts = part_stride = 0
+    if mix is not None:
+        _need(mix, "mix", torch.float32); _need(spread, "spread", torch.float32)
+        if mix.numel() != streams * streams or spread.numel() != streams or y is None:
+            raise KernelError("stream_step: the update needs [streams, streams] weights, [streams] weights and a result")
+        _need(y, "y")
+        if y.dim() == 3 or y.dtype == torch.float32 and (out is None or out.dtype != torch.float32):
+            _need(y, "y", torch.float32)
+            parts = y if y.dim() == 3 else y.unsqueeze(0)
+            if parts.shape[1:] != (total_rows, width):
+                raise KernelError("stream_step: the partial sums must be [parts, rows, width]")
+            num_parts, part_stride = parts.shape[0], parts.stride(0)
+        else:
+            if y.shape != (total_rows, width):
+                raise KernelError("stream_step: the result must be [rows, width]")
+            whole = y
+    dtype = x.dtype
+    pitch = 0
+    if gather is not None:
+        _need(gather, "gather", torch.float32)
+        if out is None or out.dim() != 2 or out.shape != (rows, width) or out.stride(1) != 1 or not out.is_cuda:
+            raise KernelError("stream_step: out must be a CUDA matrix [rows, width] with dense rows")
+        dtype, pitch = out.dtype, out.stride(0)
+        if weight is not None:
+            _need(weight, "weight", torch.float32)
+    if whole is not None:
+        if gather is not None and whole.dtype != dtype:
+            raise KernelError("stream_step: the result must be float32 or of out's dtype")
+        dtype = whole.dtype
+    if row_index is not None:
+        _need(row_index, "row_index", torch.int32)
+    lib = load_library("streams")
+    _check(lib, lib.srb_stream_step(
+        _ptr(x), _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), _ptr(mix), _ptr(spread), _ptr(gather),
+        _ptr(weight), ctypes.c_float(eps), int(norm), _ptr(out), ctypes.c_longlong(pitch), _ptr(row_index), rows, streams,
+        width, 1, dtype_code(dtype), _stream()))
+
+
+# --------------------------------------------------------------------------- linear attention over a state
+
+@traced("lightning")
+def lightning_scan(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: int, cu_rows: torch.Tensor,
+                   positions: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
+                   out: torch.Tensor, requests: int, read_only: bool = False) -> None:
+    """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v the SiLU of the row's projections.
+
+    ``proj`` [rows, *]: q heads (dim entries each) from column ``q_offset``, k heads from ``k_offset``, v heads
+    (vdim each) from ``v_offset``; ``state`` float32 [slots, heads, dim, vdim], updated in place for the slots
+    ``state_slots[request]`` (a request whose first row is at position 0 starts from zero); ``out`` float32
+    [rows, heads * vdim].  The rows of request r are ``cu_rows[r] .. cu_rows[r + 1]``."""
+    _need(positions, "positions", torch.int32); _need(cu_rows, "cu_rows", torch.int32)
+    _need(state_slots, "state_slots", torch.int32); _need(state, "state", torch.float32); _need(decay, "decay", torch.float32)
+    _need(out, "out", torch.float32)
+    if proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("lightning_scan: proj must be a CUDA matrix with dense rows")
+    _, heads, dim, vdim = state.shape
+    if decay.numel() != heads or out.shape != (proj.shape[0], heads * vdim):
+        raise KernelError("lightning_scan: shapes of the state, the decays and out do not agree")
+    if max(q_offset, k_offset) + heads * dim > proj.shape[1] or v_offset + heads * vdim > proj.shape[1]:
+        raise KernelError("lightning_scan: rows of proj are too short")
+    lib = load_library("lightning")
+    _check(lib, lib.srb_lightning_scan(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), q_offset, k_offset, v_offset, _ptr(cu_rows), _ptr(positions),
+        _ptr(state_slots), _ptr(state), _ptr(decay), _ptr(out), int(requests), heads, dim, vdim, int(read_only),
+        dtype_code(proj.dtype), _stream()))
+
+
+@traced("lightning")
+def lightning_gate_norm(o: torch.Tensor, proj: torch.Tensor, g_offset: int, weight: torch.Tensor, eps: float,
+                        out: torch.Tensor) -> None:
+    """out = o / sqrt(mean(o^2) + eps) * weight * sigmoid(g): the heads' results of a row normed together; the gate's
+    logits are the columns ``g_offset`` .. of ``proj``."""
+    _need(o, "o", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out", proj.dtype)
+    rows, width = o.shape
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[0] != rows or g_offset + width > proj.shape[1]:
+        raise KernelError("lightning_gate_norm: proj does not hold the gate's logits")
+    if out.shape != o.shape or weight.numel() != width:
+        raise KernelError("lightning_gate_norm: shapes do not agree")
+    lib = load_library("lightning")
+    _check(lib, lib.srb_lightning_gate_norm(_ptr(o), _ptr(proj), ctypes.c_longlong(proj.stride(0)), g_offset, _ptr(weight),
+                                            ctypes.c_float(eps), rows, width, _ptr(out), dtype_code(proj.dtype), _stream()))
 
 
 # --------------------------------------------------------------------------- sampling

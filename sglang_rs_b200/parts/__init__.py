@@ -5,14 +5,18 @@ from .block import PreNormBlock, SandwichBlock
 from .latent_attention import LatentAttention, LatentAttentionNames
 from .loop import PassEntry
 from .moe import RoutedExperts
-from .embedding import OutputHead, TokenEmbedding
-from .mlp import GatedMlp, GatedMlpNames
+from .embedding import OutputHead, PairTokenEmbedding, TokenEmbedding
+from .hyper import StreamBlock, StreamConnection, StreamNames, StreamSumNorm, StreamUpdate
+from .lightning import LightningAttention, LightningNames
+from .mlp import GatedMlp, GatedMlpNames, PlainMlp
 from .norm import LayerNorm, RmsNorm
-from .rope import NoPositionEncoding, RotaryEncoding
+from .rope import NoPositionEncoding, RotaryEncoding, WavelengthScaling
 
 __all__ = [
     "AttentionNames", "GroupedQueryAttention", "CacheNeed", "FeedForward", "Mixer", "Norm", "PagedKV", "Part",
     "PositionEncoding", "RequestState", "TensorSpec", "matrix_to", "scale_to", "PreNormBlock", "OutputHead",
     "TokenEmbedding", "GatedMlp", "GatedMlpNames", "RmsNorm", "NoPositionEncoding", "RotaryEncoding", "NormedDelta",
     "SandwichBlock", "LatentAttention", "LatentAttentionNames", "PassEntry", "RoutedExperts", "LayerNorm",
+    "PairTokenEmbedding", "StreamBlock", "StreamConnection", "StreamNames", "StreamSumNorm", "StreamUpdate",
+    "LightningAttention", "LightningNames", "PlainMlp", "WavelengthScaling",
 ]

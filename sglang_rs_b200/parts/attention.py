@@ -7,6 +7,12 @@ row's slot; scores (q . k) * scale over the keys the row may see, kv head = q he
 (n_q / n_kv) (crates/sglang-kernel/src/cpu.rs:475-479); softmax; weighted sum of v; output
 projection.  q, k and v come from one product with the row-wise concatenation of the
 three matrices, made at load time.
+
+Two variations that other designs use, both off by default: ``names.v`` None means there is no value
+projection and the value of a key is the key itself as projected, before the rotation (the product then
+holds q and k only, and the fused kernel stores the unrotated key in the value pool); ``chunk`` makes a row
+see, of the keys up to its own, only those of its own chunk of ``chunk`` positions (chunks counted from
+position 0 of the sequence, whatever portion of a prompt brought the row).
 """
 from __future__ import annotations
 
@@ -23,7 +29,7 @@ from .base import Mixer, PagedKV, PositionEncoding, TensorSpec, matrix_to, scale
 class AttentionNames:
     q: str
     k: str
-    v: str
+    v: Optional[str]
     o: str
     q_norm: Optional[str] = None
     k_norm: Optional[str] = None
@@ -42,7 +48,7 @@ class GroupedQueryAttention(Mixer):
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  position: PositionEncoding, names: AttentionNames, *, qk_norm_eps: Optional[float] = None,
-                 window: Optional[int] = None):
+                 window: Optional[int] = None, chunk: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         if not 0 < head_dim <= self.MAX_HEAD_DIM:
@@ -53,6 +59,12 @@ class GroupedQueryAttention(Mixer):
         self.hidden, self.n_q, self.n_kv, self.d = int(hidden), int(num_heads), int(num_kv_heads), int(head_dim)
         self.scale, self.position, self.names = float(scale), position, names
         self.qk_norm_eps, self.window = qk_norm_eps, window
+        if chunk is not None and chunk <= 0:
+            raise ValueError(f"a chunk of {chunk} positions")
+        self.chunk = chunk
+        self.values_from_keys = names.v is None
+        if self.values_from_keys and names.v_bias:
+            raise ValueError("values that are the keys have no bias of their own")
         self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_norm = self.k_norm = None
 
     def cache_need(self) -> PagedKV:
@@ -66,9 +78,10 @@ class GroupedQueryAttention(Mixer):
         specs = {
             n.q: TensorSpec((self.n_q * self.d, self.hidden)),
             n.k: TensorSpec((self.n_kv * self.d, self.hidden)),
-            n.v: TensorSpec((self.n_kv * self.d, self.hidden)),
             n.o: TensorSpec((self.hidden, self.n_q * self.d)),
         }
+        if n.v:
+            specs[n.v] = TensorSpec((self.n_kv * self.d, self.hidden))
         if n.q_norm:
             specs[n.q_norm] = TensorSpec((self.d,), "scale")
         if n.k_norm:
@@ -82,14 +95,15 @@ class GroupedQueryAttention(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         n = self.names
-        self.w_qkv = matrix_to(torch.cat([tensors[n.q], tensors[n.k], tensors[n.v]], dim=0), device, dtype)
+        stacked = [tensors[n.q], tensors[n.k]] + ([tensors[n.v]] if n.v else [])
+        self.w_qkv = matrix_to(torch.cat(stacked, dim=0), device, dtype)
         self.w_o = matrix_to(tensors[n.o], device, dtype)
         self.q_norm = scale_to(tensors[n.q_norm], device) if n.q_norm else None
         self.k_norm = scale_to(tensors[n.k_norm], device) if n.k_norm else None
         if n.q_bias or n.k_bias or n.v_bias:
             parts = []
             for name, width in ((n.q_bias, self.n_q * self.d), (n.k_bias, self.n_kv * self.d),
-                                (n.v_bias, self.n_kv * self.d)):
+                                (n.v_bias, self.n_kv * self.d))[:2 if self.values_from_keys else 3]:
                 parts.append(tensors[name].to(torch.float32) if name else torch.zeros(width))
             self.b_qkv = scale_to(torch.cat(parts), device)
         self.b_o = scale_to(tensors[n.o_bias], device) if n.o_bias else None
@@ -100,10 +114,10 @@ class GroupedQueryAttention(Mixer):
         kernel applies from a frequency table (an encoding that computes its angles in Python keeps the
         part-by-part path)."""
         from ..ops.records import SxAttention, linear_record
-        if self.w_qkv is None or not self.position.fused:
+        if self.w_qkv is None or not self.position.fused or self.values_from_keys or self.chunk:
             return None
         rotary = self.position.fused_rotary()
-        if rotary is not None and (rotary.angles is not None or rotary.inv_freq is None):
+        if rotary is not None and (rotary.angles is not None or rotary.inv_freq is None or rotary.magnitude != 1.0):
             return None
         return SxAttention(
             linear_record(self.w_qkv, self.b_qkv), linear_record(self.w_o, self.b_o),
@@ -127,18 +141,20 @@ class GroupedQueryAttention(Mixer):
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
             rotary.inv_freq if rotary else None, rotary.rotary_dim if rotary else 0,
             rotary.interleaved if rotary else False, self.n_q, self.n_kv, self.d, ctx.error_word,
-            angles=rotary.angles(ctx.positions) if rotary is not None and rotary.angles is not None else None)
+            angles=rotary.angles(ctx.positions) if rotary is not None and rotary.angles is not None else None,
+            magnitude=rotary.magnitude if rotary is not None else 1.0, values_from_keys=self.values_from_keys)
         out = torch.empty_like(q)
+        chunk = self.chunk or 0
         for launch in batch.launches:
             b, e = launch.begin, launch.end
             if launch.wide_tiles is not None and ops.tiled_attention_tc_takes(q.dtype, self.n_q, self.n_kv, self.d,
                                                                               cache.k_pool.shape[2]):
                 ops.tiled_attention_tc(q, cache.k_pool, cache.v_pool, out, launch.wide_tiles, batch.block_table,
-                                       scale=self.scale, window=self.window or 0, error_word=ctx.error_word)
+                                       scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk)
                 continue
             if launch.tiles is not None and ops.tiled_attention_takes(q.dtype, self.n_q, self.n_kv, self.d):
                 ops.tiled_attention(q, cache.k_pool, cache.v_pool, out, launch.tiles, batch.block_table,
-                                    scale=self.scale, window=self.window or 0, error_word=ctx.error_word)
+                                    scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk)
                 continue
             if (launch.tiles is None and launch.split_size and batch.counters is not None
                     and batch.counters.numel() >= (e - b) * self.n_kv
@@ -147,12 +163,12 @@ class GroupedQueryAttention(Mixer):
                                      ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                      window=self.window or 0, scratch_acc=batch.scratch_acc,
                                      scratch_ml=batch.scratch_ml, counters=batch.counters,
-                                     error_word=ctx.error_word, max_keys=launch.max_keys)
+                                     error_word=ctx.error_word, max_keys=launch.max_keys, chunk=chunk)
                 continue
             ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                 window=self.window or 0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
-                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word)
+                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word, chunk=chunk)
         return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
                           partial_ok=True)

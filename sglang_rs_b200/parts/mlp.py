@@ -10,7 +10,7 @@ a name there, not a change to a product kernel.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Mapping
+from typing import Dict, Mapping, Optional
 
 import torch
 
@@ -20,7 +20,7 @@ from .base import FeedForward, TensorSpec, matrix_to
 
 @dataclass(frozen=True)
 class GatedMlpNames:
-    gate: str
+    gate: Optional[str]      # None: a feed-forward without a gate (routed experts take such names)
     up: str
     down: str
 
@@ -55,4 +55,33 @@ class GatedMlp(FeedForward):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         error_word = ctx.error_word if ctx is not None else None
         act = ops.gated_product(x, self.w_gate_up, self.inner, error_word, self.activation)
+        return ops.linear(act, self.w_down, error_word=error_word, partial_ok=True)
+
+
+class PlainMlp(FeedForward):
+    """A feed-forward without a gate: down( act(up(x)) ).  The activation rides in the epilogue of the first
+    product where the product kernel has one (few rows, bfloat16), else a kernel of its own follows it.  With
+    ``float_result`` the second product keeps its 32-bit accumulator (for a consumer that adds it to other 32-bit
+    terms)."""
+    graph_safe = True
+
+    def __init__(self, hidden: int, inner: int, activation: str, up_name: str, down_name: str, float_result: bool = False):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
+        self.hidden, self.inner, self.activation = int(hidden), int(inner), activation
+        self.up_name, self.down_name, self.float_result = up_name, down_name, bool(float_result)
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.up_name: TensorSpec((self.inner, self.hidden)), self.down_name: TensorSpec((self.hidden, self.inner))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        self.w_up = matrix_to(tensors[self.up_name], device, dtype)
+        self.w_down = matrix_to(tensors[self.down_name], device, dtype)
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        error_word = ctx.error_word if ctx is not None else None
+        act = ops.activated_product(x, self.w_up, self.activation, error_word)
+        if self.float_result:
+            return ops.linear(act, self.w_down, out_dtype=torch.float32, error_word=error_word)
         return ops.linear(act, self.w_down, error_word=error_word, partial_ok=True)

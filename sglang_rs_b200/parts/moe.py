@@ -7,15 +7,20 @@ gated feed-forward without biases: W_down (act(W_gate h) * (W_up h)).  The exper
 load ([experts, ...]; gate rows over up rows); the whole part is a handful of launches that decide nothing on the host (``ops.routed_experts``),
 so decode steps can be captured.  The result is 32-bit: the weighted sum is taken in 32-bit and goes to
 the residual sum (or the norm ahead of it) unrounded.
+
+Variations, all off by default: experts without a gate, W_down act(W_up h) (``expert_names`` then gives
+``GatedMlpNames`` with ``gate`` None); a bias on the router's logits (``router_bias_name``), added before the
+choice; an expert that every row shares (``shared``: a feed-forward whose 32-bit result is the first term of
+the sum).  A softmax over the chosen logits only is the same as ``renormalize`` over the softmax of all.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Mapping
+from typing import Callable, Dict, Mapping, Optional
 
 import torch
 
 from .. import ops
-from .base import FeedForward, TensorSpec, matrix_to
+from .base import FeedForward, TensorSpec, matrix_to, scale_to
 from .mlp import GatedMlpNames
 
 
@@ -23,7 +28,8 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden: int, inner: int, experts: int, top: int, activation: str, router_name: str,
-                 expert_names: Callable[[int], GatedMlpNames], renormalize: bool = False):
+                 expert_names: Callable[[int], GatedMlpNames], renormalize: bool = False, *,
+                 router_bias_name: Optional[str] = None, shared: Optional[FeedForward] = None):
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
         if not 0 < top <= experts:
@@ -33,12 +39,21 @@ class RoutedExperts(FeedForward):
         self.hidden, self.inner, self.experts, self.top = int(hidden), int(inner), int(experts), int(top)
         self.activation, self.router_name, self.renormalize = activation, router_name, bool(renormalize)
         self.names = [expert_names(e) for e in range(self.experts)]
-        self.router = self.w_gate_up = self.w_down = None
+        self.gated = self.names[0].gate is not None
+        if any((n.gate is not None) != self.gated for n in self.names):
+            raise ValueError("the experts of one layer have a gate or have none, all alike")
+        self.router_bias_name, self.shared = router_bias_name, shared
+        self.router = self.w_gate_up = self.w_down = self.router_bias = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.router_name: TensorSpec((self.experts, self.hidden))}
+        if self.router_bias_name:
+            specs[self.router_bias_name] = TensorSpec((self.experts,))
+        if self.shared is not None:
+            specs.update(self.shared.tensor_specs())
         for n in self.names:
-            specs[n.gate] = TensorSpec((self.inner, self.hidden))
+            if self.gated:
+                specs[n.gate] = TensorSpec((self.inner, self.hidden))
             specs[n.up] = TensorSpec((self.inner, self.hidden))
             specs[n.down] = TensorSpec((self.hidden, self.inner))
         return specs
@@ -46,10 +61,20 @@ class RoutedExperts(FeedForward):
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.router = matrix_to(tensors[self.router_name], device, dtype)
         # per expert the gate rows over the up rows: the two matrices of a tile then lie a fixed distance apart
-        self.w_gate_up = matrix_to(torch.stack([torch.cat([tensors[n.gate], tensors[n.up]], dim=0) for n in self.names]),
-                                   device, dtype)
+        if self.gated:
+            stacked = [torch.cat([tensors[n.gate], tensors[n.up]], dim=0) for n in self.names]
+        else:
+            stacked = [tensors[n.up] for n in self.names]
+        self.w_gate_up = matrix_to(torch.stack(stacked), device, dtype)
+        self.router_bias = scale_to(tensors[self.router_bias_name], device) if self.router_bias_name else None
+        if self.shared is not None:
+            self.shared.load(tensors, device, dtype)
         self.w_down = matrix_to(torch.stack([tensors[n.down] for n in self.names]), device, dtype)
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        base = self.shared.forward(ctx, x) if self.shared is not None else None
+        if base is not None and (base.dtype != torch.float32 or base.dim() != 2):
+            raise TypeError("the shared expert must give a 32-bit result [rows, width]")
         return ops.routed_experts(x, self.router, self.w_gate_up, self.w_down, self.top, self.activation,
-                                  self.renormalize, ctx.error_word)
+                                  self.renormalize, ctx.error_word, gated=self.gated, router_bias=self.router_bias,
+                                  base=base)
