@@ -156,7 +156,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel", "tosivik"))
     parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
@@ -168,6 +168,8 @@ def main() -> int:
                         help="length of the prompt of --only-prefill (the bench line always uses 2,048)")
     parser.add_argument("--requests", type=int, default=128, help="--mode serve: number of requests")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--width", type=int, default=2048, choices=(1024, 2048, 4096),
+                        help="--mode tosivik: the model's width; heads, feed-forwards and the Qwen3 shape beside it follow")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -182,6 +184,8 @@ def main() -> int:
 
     if args.mode == "gegepel":
         return gegepel_beside_qwen3(args, warmup)
+    if args.mode == "tosivik":
+        return tosivik_beside_qwen3(args, warmup)
 
     if args.mode == "timeline":
         # the kernels of a decode step, built with marks that record when each block starts, stops waiting for the
@@ -807,10 +811,6 @@ def gegepel_beside_qwen3(args, warmup) -> int:
     """``--mode gegepel``: prefill and decode of a Gegepel model with layers of a real model's size (random weights),
     beside the Qwen3 shape of equal width, both through the step function: device time per step, tokens per second,
     and the device time per kernel class of an uncaptured step (CUDA events around every op)."""
-    import torch
-    from sglang_rs_b200.engine.engine import Engine
-    from sglang_rs_b200.engine.runner import StepEntry
-    from sglang_rs_b200.ops import trace
     layers = args.layers if args.layers is not None else 4
     vocab = 32768
     block = {"type": "latent_attention", "mixer": GEGEPEL_MIXER, "mlp": GEGEPEL_MLP}
@@ -820,12 +820,61 @@ def gegepel_beside_qwen3(args, warmup) -> int:
                     "loop": {"start": 1, "stop": min(3, layers), "times": 2} if layers >= 2 else None},
         "qwen3": {**model_config("qwen3-1.7b", layers, 1 << 16), "vocab_size": vocab},
     }
+    note = {"layers": layers, "width": GEGEPEL_WIDTH, "vocab": vocab, "gegepel_mixer": GEGEPEL_MIXER, "gegepel_mlp": GEGEPEL_MLP,
+            "layer_runs": {"gegepel": layers + (min(3, layers) - 1 if layers >= 2 else 0), "qwen3": layers}}
+    return designs_side_by_side(args, warmup, "gegepel", designs, vocab, note)
+
+
+def tosivik_layers(width: int, count: int):
+    """Layers of a real model's size at ``width``: heads of 128 entries, four query heads per kv head, half of each head
+    rotated with stretched wavelengths, chunks of 1,024 positions; linear attention with states of 128 x 128 per head and
+    decays spread over the heads; a feed-forward of three times the width, or 64 experts of 11/16 of the width (6 chosen)
+    beside a shared one.  The four kinds alternate as lightning + dense, lightning + experts, attention + dense, attention
+    + experts."""
+    heads = width // 128
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 1.0 / math.sqrt(128),
+                 "mask": {"size": 1024},
+                 "rot": {"base": 50000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lightning = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-3 - 5 * h / heads) for h in range(heads)]}
+    dense = {"kind": "dense", "ff": 3 * width}
+    experts = {"kind": "moe", "router": {"experts": 64, "top": 6}, "expert": {"ff": 11 * width // 16},
+               "shared": {"ff": 11 * width // 16}}
+    kinds = [("lightning", lightning, dense), ("lightning", lightning, experts), ("attention", attention, dense),
+             ("attention", attention, experts)]
+    return [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer, mlp in (kinds[i % 4] for i in range(count))]
+
+
+def tosivik_beside_qwen3(args, warmup) -> int:
+    """``--mode tosivik``: prefill and decode of a Tosivik model with layers of a real model's size (random weights),
+    beside the Qwen3 shape of equal width, as ``--mode gegepel`` does for that design.  ``--width`` 1024, 2048 or 4096."""
+    layers = args.layers if args.layers is not None else 4
+    vocab = 32768
+    beside = {1024: "qwen3-0.6b", 2048: "qwen3-1.7b", 4096: "qwen3-8b"}[args.width]
+    if beside not in SHAPES:
+        beside = "qwen3-1.7b"
+    designs = {
+        "tosivik": {"architecture": "Tosivik", "vocab": vocab, "width": args.width, "streams": 4, "logit_softcap": 30.0,
+                    "embedding": {"scale": math.sqrt(args.width), "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+                    "norm": {"eps": 1e-5}, "layers": tosivik_layers(args.width, layers)},
+        "qwen3": {**model_config(beside, layers, 1 << 16), "vocab_size": vocab},
+    }
+    note = {"layers": layers, "width": args.width, "vocab": vocab, "tosivik_layers": designs["tosivik"]["layers"][:4],
+            "streams": 4, "qwen3_shape": beside}
+    return designs_side_by_side(args, warmup, "tosivik", designs, vocab, note)
+
+
+def designs_side_by_side(args, warmup, mode, designs, vocab, note) -> int:
+    """Prefill of ``--prefill-tokens`` tokens and decode at ``--batch`` and ``--context`` of each design of ``designs``
+    through the step function: device time per step, tokens per second, and the device time per kernel class of an
+    uncaptured step."""
+    import torch
+    from sglang_rs_b200.engine.engine import Engine
+    from sglang_rs_b200.engine.runner import StepEntry
+    from sglang_rs_b200.ops import trace
     peak, source = peaks()
     length, batch, context = args.prefill_tokens, args.batch, args.context
-    out = {"mode": "gegepel", "dtype": "bf16", "data": "synthetic (random weights and tokens)",
-           "config": {"layers": layers, "width": GEGEPEL_WIDTH, "vocab": vocab, "prefill_tokens": length, "global_batch": batch,
-                      "seq_len": context, "gegepel_mixer": GEGEPEL_MIXER, "gegepel_mlp": GEGEPEL_MLP,
-                      "layer_runs": {"gegepel": layers + (min(3, layers) - 1 if layers >= 2 else 0), "qwen3": layers}},
+    out = {"mode": mode, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+           "config": {"prefill_tokens": length, "global_batch": batch, "seq_len": context, **note},
            "peaks": {"source": source, **{k: peak[k] for k in ("hbm_gbs", "bf16_tflops") if k in peak}}}
     for name, document in designs.items():
         torch.manual_seed(0)

@@ -213,3 +213,32 @@ def logits(tokens, tensors, doc):
     out = rms_norm(x, _t(tensors, "final.norm"), doc["norm"]["eps"]) @ _t(tensors, "head").T
     cap = doc.get("logit_softcap")
     return cap * torch.tanh(out / cap) if cap else out
+
+
+# ----------------------------------------------------------------------------- for tests of single kernels
+
+def attend(q, k, v, scale, chunk, first_position):
+    """q [rows, heads, d] are the positions first_position .. of a sequence whose keys k and values v
+    [keys, kv heads, d] start at position 0; returns [rows, heads, d]."""
+    rows, heads, _ = q.shape
+    per = heads // k.shape[1]
+    out = torch.zeros(rows, heads, v.shape[2], dtype=F)
+    for r in range(rows):
+        pos = first_position + r
+        lo = pos // chunk * chunk if chunk else 0
+        for h in range(heads):
+            s = (k[lo:pos + 1, h // per] @ q[r, h]) * scale
+            out[r, h] = torch.softmax(s, 0) @ v[lo:pos + 1, h // per]
+    return out
+
+
+def linear_attention(q, k, v, decay, state):
+    """Token by token from ``state`` [heads, dim, vdim]; q, k [n, heads, dim], v [n, heads, vdim], already
+    activated.  Returns the results [n, heads, vdim] and the state after the last token."""
+    state = state.clone()
+    out = torch.zeros(q.shape[0], q.shape[1], v.shape[2], dtype=F)
+    d = torch.tensor(decay, dtype=F)[:, None, None]
+    for t in range(q.shape[0]):
+        state = d * state + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+    return out, state
