@@ -192,3 +192,415 @@ extern "C" int srb_lightning_gate_norm(const float* o, const void* proj, long lo
   SRB_LAUNCH_CHECK("lightning_gate_norm");
   return SRB_OK;
 }
+
+// ---- prompt portions in bfloat16: chunks in parallel, products on the tensor cores -------------------------------
+// The rows of every request are cut into chunks of LC_TOKENS tokens (from the request's first row of the step).  Three
+// kernels behind one pass that replaces the q, k and v columns of the projection by their SiLU (rounded to bfloat16):
+//   1. per (chunk, head) the chunk's own contribution to the state, U = sum_j decay^(n-1-j) k_j v_j^T        (parallel)
+//   2. per (request, head, entry) the states before every chunk, S_(c+1) = decay^(n_c) S_c + U_c, walking the
+//      request's chunks in order; U_c is replaced by S_c, and the request's slot receives the last state     (cheap)
+//   3. per (chunk, head) the results o_t = decay^(t+1) S_c^T q_t + sum_(j<=t) decay^(t-j) (q_t . k_j) v_j    (parallel)
+// q, k, v are the SiLU of the projections rounded to bfloat16 (mma.sync m16n8k16, 32-bit accumulation).  Rows come in
+// by 16-byte loads, all of a thread's loads in flight before the first is used.  Whatever is
+// 32-bit by the design and has to be an operand of a product (keys times powers of the decay, decayed scores, the
+// state) goes in as the sum of two bfloat16 numbers, its rounding and the rounding of the rest, in two products: 16
+// bits of mantissa survive.  Operands lie in shared memory with the contraction index contiguous and rows padded by
+// 16 bytes, so a fragment is four (or two) conflict-free 32-bit loads.
+#include "mma_helpers.cuh"
+#define LC_TOKENS 64
+#define LC_THREADS 128
+#define LC_PAD 8
+
+struct LightningChunkArgs {
+  const __nv_bfloat16* proj;
+  long long pitch;
+  int q_offset, k_offset, v_offset;
+  const int* cu_rows;
+  const int* positions;
+  const int* state_slots;
+  float* state;              // [slots, heads, dim, vdim]
+  const float* decay;
+  float* chunk_states;       // [chunks, heads, dim, vdim]: U of a chunk, then the state before it
+  float* out;                // [rows, heads * vdim]
+  int requests, heads, read_only;
+};
+
+// the request and the chunk of it that block `index` works on; false: there is no such chunk
+__device__ __forceinline__ bool lc_find(const LightningChunkArgs& a, int index, int& request, int& row0, int& n) {
+  int first = 0;
+  for (request = 0; request < a.requests; ++request) {
+    const int begin = a.cu_rows[request], rows = a.cu_rows[request + 1] - begin;
+    const int chunks = (rows + LC_TOKENS - 1) / LC_TOKENS;
+    if (index < first + chunks) {
+      row0 = begin + (index - first) * LC_TOKENS;
+      n = min(LC_TOKENS, begin + rows - row0);
+      return true;
+    }
+    first += chunks;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void lc_powers(float* power, float decay) {     // power[m] = decay^m, m = 0 .. LC_TOKENS
+  if (threadIdx.x == 0) {
+    float p = 1.f;
+    for (int m = 0; m <= LC_TOKENS; ++m) {
+      power[m] = p;
+      p *= decay;
+    }
+  }
+}
+
+__device__ __forceinline__ unsigned lc_word(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned*>(p); }
+
+__device__ __forceinline__ void lc_split(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(v);
+  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+struct Bf16x8 { __nv_bfloat16 v[8]; };
+__device__ __forceinline__ Bf16x8 lc_load8(const __nv_bfloat16* p, bool live) {
+  Bf16x8 r;
+  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+  if (live) raw = *reinterpret_cast<const uint4*>(p);
+  *reinterpret_cast<uint4*>(r.v) = raw;
+  return r;
+}
+
+// columns [begin, begin + count) of every row: x <- SiLU(x), rounded once; eight values a thread
+__global__ void lightning_activate_kernel(__nv_bfloat16* proj, long long pitch, int rows, int begin0, int count0, int begin1,
+                                          int count1, int begin2, int count2) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int per_row = (count0 + count1 + count2) / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)rows * per_row;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / per_row);
+    int at = (int)(i - (long long)row * per_row) * 8;
+    int column;
+    if (at < count0) column = begin0 + at;
+    else if (at < count0 + count1) column = begin1 + at - count0;
+    else column = begin2 + at - count0 - count1;
+    __nv_bfloat16* p = proj + (size_t)row * pitch + column;
+    Bf16x8 x = lc_load8(p, true);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x.v[k] = __float2bfloat16_rn(la_silu(__bfloat162float(x.v[k])));
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(x.v);
+  }
+}
+
+// Loads a [LC_TOKENS, WIDTH] slice of the (activated) projection, transposed, into `dst` [WIDTH][TP]: consecutive lanes
+// take consecutive tokens, so the 2-byte stores of a warp fall into consecutive words.  `scale` (or null) gives a
+// factor per token; with it the product goes in as two bfloat16 numbers (dst, dst_lo).
+template <int WIDTH>
+__device__ __forceinline__ void lc_load_transposed(const __nv_bfloat16* src, long long pitch, int n, const float* scale,
+                                                   int scale_last, __nv_bfloat16* dst, __nv_bfloat16* dst_lo) {
+  constexpr int TP = LC_TOKENS + LC_PAD, ITEMS = LC_TOKENS * WIDTH / 8, PER = ITEMS / LC_THREADS;
+  Bf16x8 x[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int item = threadIdx.x + i * LC_THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
+    x[i] = lc_load8(src + (size_t)j * pitch + d0, j < n);
+  }
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int item = threadIdx.x + i * LC_THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
+    const float factor = (scale && j < n) ? scale[scale_last - j] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (scale) {
+        __nv_bfloat16 hi, lo;
+        lc_split(factor * __bfloat162float(x[i].v[k]), hi, lo);
+        dst[(d0 + k) * TP + j] = hi;
+        dst_lo[(d0 + k) * TP + j] = lo;
+      } else {
+        dst[(d0 + k) * TP + j] = x[i].v[k];
+      }
+    }
+  }
+}
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(LC_THREADS) lightning_chunk_states_kernel(LightningChunkArgs a) {
+  constexpr int TP = LC_TOKENS + LC_PAD;
+  extern __shared__ __align__(16) unsigned char lc_smem[];
+  __nv_bfloat16* kt_hi = reinterpret_cast<__nv_bfloat16*>(lc_smem);      // [DIM][TP]: decay^(n-1-j) k_j[d], rounded
+  __nv_bfloat16* kt_lo = kt_hi + DIM * TP;                               // ... and what the rounding left
+  __nv_bfloat16* vt = kt_lo + DIM * TP;                                  // [VDIM][TP]
+  __shared__ float power[LC_TOKENS + 1];
+  srb_launch_dependents();
+  const int head = blockIdx.y;
+  lc_powers(power, a.decay[head]);
+  srb_grid_dependency_wait();
+  int request, row0, n;
+  if (!lc_find(a, blockIdx.x, request, row0, n)) return;
+  __syncthreads();
+  lc_load_transposed<DIM>(a.proj + (size_t)row0 * a.pitch + a.k_offset + head * DIM, a.pitch, n, power, n - 1, kt_hi, kt_lo);
+  lc_load_transposed<VDIM>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int MT = DIM / 64;                 // m16 tiles per warp: the warp owns DIM / 4 rows of U
+  constexpr int NT = VDIM / 8;
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[m][nt][0] = acc[m][nt][1] = acc[m][nt][2] = acc[m][nt][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < LC_TOKENS / 16; ++kk) {
+    unsigned ah[MT][4], al[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const int row = warp * (DIM / 4) + m * 16 + g, col = kk * 16 + 2 * t;
+      ah[m][0] = lc_word(kt_hi + row * TP + col);       al[m][0] = lc_word(kt_lo + row * TP + col);
+      ah[m][1] = lc_word(kt_hi + (row + 8) * TP + col); al[m][1] = lc_word(kt_lo + (row + 8) * TP + col);
+      ah[m][2] = lc_word(kt_hi + row * TP + col + 8);   al[m][2] = lc_word(kt_lo + row * TP + col + 8);
+      ah[m][3] = lc_word(kt_hi + (row + 8) * TP + col + 8); al[m][3] = lc_word(kt_lo + (row + 8) * TP + col + 8);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const __nv_bfloat16* b = vt + (nt * 8 + g) * TP + kk * 16 + 2 * t;
+      const unsigned b0 = lc_word(b), b1 = lc_word(b + 8);
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        mma_bf16(acc[m][nt], ah[m], b0, b1);
+        mma_bf16(acc[m][nt], al[m], b0, b1);
+      }
+    }
+  }
+  float* u = a.chunk_states + ((size_t)blockIdx.x * a.heads + head) * DIM * VDIM;
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int row = warp * (DIM / 4) + m * 16 + g, col = nt * 8 + 2 * t;
+      *reinterpret_cast<float2*>(u + (size_t)row * VDIM + col) = make_float2(acc[m][nt][0], acc[m][nt][1]);
+      *reinterpret_cast<float2*>(u + (size_t)(row + 8) * VDIM + col) = make_float2(acc[m][nt][2], acc[m][nt][3]);
+    }
+}
+
+// One thread per entry of a head's state: the request's chunks in order.
+__global__ void lightning_chunk_prefix_kernel(LightningChunkArgs a, int entries) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x, head = blockIdx.y, request = blockIdx.z;
+  if (e >= entries) return;
+  int first = 0;
+  for (int r = 0; r < request; ++r) first += (a.cu_rows[r + 1] - a.cu_rows[r] + LC_TOKENS - 1) / LC_TOKENS;
+  const int begin = a.cu_rows[request], rows = a.cu_rows[request + 1] - begin;
+  if (rows <= 0) return;
+  const float decay = a.decay[head];
+  float whole = 1.f;                                   // decay^LC_TOKENS, as the other kernels' tables have it
+  for (int m = 0; m < LC_TOKENS; ++m) whole *= decay;
+  float* state = a.state + ((size_t)a.state_slots[request] * a.heads + head) * entries + e;
+  float s = a.positions[begin] == 0 ? 0.f : *state;
+  const int chunks = (rows + LC_TOKENS - 1) / LC_TOKENS;
+  const size_t step = (size_t)a.heads * entries;
+  float* u = a.chunk_states + ((size_t)first * a.heads + head) * entries + e;
+  for (int c0 = 0; c0 < chunks; c0 += 8) {
+    float own[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (c0 + k < chunks) own[k] = u[(size_t)(c0 + k) * step];       // eight loads in flight
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = c0 + k;
+      if (c >= chunks) break;
+      const int n = min(LC_TOKENS, rows - c * LC_TOKENS);
+      float factor = whole;
+      if (n < LC_TOKENS) {
+        factor = 1.f;
+        for (int m = 0; m < n; ++m) factor *= decay;
+      }
+      u[(size_t)c * step] = s;
+      s = fmaf(factor, s, own[k]);
+    }
+  }
+  if (!a.read_only) *state = s;
+}
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(LC_THREADS) lightning_chunk_outputs_kernel(LightningChunkArgs a) {
+  constexpr int DP = DIM + LC_PAD, TP = LC_TOKENS + LC_PAD;
+  extern __shared__ __align__(16) unsigned char lc_smem[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lc_smem);          // [LC_TOKENS][DP]
+  __nv_bfloat16* ks = qs + LC_TOKENS * DP;                                // [LC_TOKENS][DP]
+  __nv_bfloat16* vt = ks + LC_TOKENS * DP;                                // [VDIM][TP]
+  __nv_bfloat16* st_hi = vt + VDIM * TP;                                  // [VDIM][DP]: the state before the chunk, transposed
+  __nv_bfloat16* st_lo = st_hi + VDIM * DP;
+  __shared__ float power[LC_TOKENS + 1];
+  srb_launch_dependents();
+  const int head = blockIdx.y;
+  lc_powers(power, a.decay[head]);
+  srb_grid_dependency_wait();
+  int request, row0, n;
+  if (!lc_find(a, blockIdx.x, request, row0, n)) return;
+  {
+    // q and k as they lie: 16-byte pieces, a row's pieces in consecutive lanes
+    constexpr int PIECES = LC_TOKENS * DIM / 8, PER = PIECES / LC_THREADS;
+    Bf16x8 xq[PER], xk[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int piece = threadIdx.x + i * LC_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
+      const __nv_bfloat16* row = a.proj + (size_t)(row0 + j) * a.pitch + head * DIM + d0;
+      xq[i] = lc_load8(row + a.q_offset, j < n);
+      xk[i] = lc_load8(row + a.k_offset, j < n);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int piece = threadIdx.x + i * LC_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
+      *reinterpret_cast<uint4*>(qs + j * DP + d0) = *reinterpret_cast<const uint4*>(xq[i].v);
+      *reinterpret_cast<uint4*>(ks + j * DP + d0) = *reinterpret_cast<const uint4*>(xk[i].v);
+    }
+  }
+  lc_load_transposed<VDIM>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  {
+    // the state before the chunk, [d][c] floats, into [c][d] as two bfloat16 numbers: consecutive lanes take
+    // consecutive d, four columns each
+    const float* before = a.chunk_states + ((size_t)blockIdx.x * a.heads + head) * DIM * VDIM;
+    constexpr int ITEMS = DIM * VDIM / 4, BATCH = 8;
+    for (int first = 0; first < ITEMS; first += BATCH * LC_THREADS) {
+      float4 x[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int item = first + threadIdx.x + i * LC_THREADS, d = item % DIM, c0 = item / DIM * 4;
+        x[i] = *reinterpret_cast<const float4*>(before + (size_t)d * VDIM + c0);
+      }
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int item = first + threadIdx.x + i * LC_THREADS, d = item % DIM, c0 = item / DIM * 4;
+        const float v[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          __nv_bfloat16 hi, lo;
+          lc_split(v[k], hi, lo);
+          st_hi[(c0 + k) * DP + d] = hi;
+          st_lo[(c0 + k) * DP + d] = lo;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int NT = VDIM / 8, ST = LC_TOKENS / 8;
+  const int r0 = warp * 16 + g, r1 = r0 + 8;              // this thread's two rows (tokens) of the chunk
+  // what the state before the chunk gives: q_t S, then times decay^(t+1)
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  float score[ST][4];
+#pragma unroll
+  for (int nt = 0; nt < ST; ++nt) score[nt][0] = score[nt][1] = score[nt][2] = score[nt][3] = 0.f;
+#pragma unroll 2
+  for (int kk = 0; kk < DIM / 16; ++kk) {
+    unsigned qa[4];
+    const int col = kk * 16 + 2 * t;
+    qa[0] = lc_word(qs + r0 * DP + col);
+    qa[1] = lc_word(qs + r1 * DP + col);
+    qa[2] = lc_word(qs + r0 * DP + col + 8);
+    qa[3] = lc_word(qs + r1 * DP + col + 8);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int at = (nt * 8 + g) * DP + col;
+      mma_bf16(acc[nt], qa, lc_word(st_hi + at), lc_word(st_hi + at + 8));
+      mma_bf16(acc[nt], qa, lc_word(st_lo + at), lc_word(st_lo + at + 8));
+    }
+#pragma unroll
+    for (int nt = 0; nt < ST; ++nt) {
+      const int at = (nt * 8 + g) * DP + col;
+      mma_bf16(score[nt], qa, lc_word(ks + at), lc_word(ks + at + 8));
+    }
+  }
+  const float carry0 = power[min(r0, LC_TOKENS - 1) + 1], carry1 = power[min(r1, LC_TOKENS - 1) + 1];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    acc[nt][0] *= carry0; acc[nt][1] *= carry0;
+    acc[nt][2] *= carry1; acc[nt][3] *= carry1;
+  }
+  // the chunk's own tokens: decayed scores of the keys up to the row's own, as two bfloat16 operands
+#pragma unroll
+  for (int kj = 0; kj < LC_TOKENS / 16; ++kj) {
+    unsigned hi[4], lo[4];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int nt = 2 * kj + half, j0 = nt * 8 + 2 * t;
+      float v[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = c < 2 ? r0 : r1, j = j0 + (c & 1);
+        v[c] = (j <= r && r < n) ? score[nt][c] * power[r - j] : 0.f;
+      }
+      __nv_bfloat16 h[4], l[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) lc_split(v[c], h[c], l[c]);
+      hi[half * 2] = pack_bf16(__bfloat162float(h[0]), __bfloat162float(h[1]));
+      hi[half * 2 + 1] = pack_bf16(__bfloat162float(h[2]), __bfloat162float(h[3]));
+      lo[half * 2] = pack_bf16(__bfloat162float(l[0]), __bfloat162float(l[1]));
+      lo[half * 2 + 1] = pack_bf16(__bfloat162float(l[2]), __bfloat162float(l[3]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const __nv_bfloat16* b = vt + (nt * 8 + g) * TP + kj * 16 + 2 * t;
+      const unsigned b0 = lc_word(b), b1 = lc_word(b + 8);
+      mma_bf16(acc[nt], hi, b0, b1);
+      mma_bf16(acc[nt], lo, b0, b1);
+    }
+  }
+  const int out_pitch = a.heads * VDIM;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int col = head * VDIM + nt * 8 + 2 * t;
+    if (r0 < n) *reinterpret_cast<float2*>(a.out + (size_t)(row0 + r0) * out_pitch + col) = make_float2(acc[nt][0], acc[nt][1]);
+    if (r1 < n) *reinterpret_cast<float2*>(a.out + (size_t)(row0 + r1) * out_pitch + col) = make_float2(acc[nt][2], acc[nt][3]);
+  }
+}
+
+template <int DIM, int VDIM>
+static int launch_lightning_chunks(const LightningChunkArgs& a, int rows, int chunks, cudaStream_t s) {
+  const size_t smem1 = (size_t)(2 * DIM + VDIM) * (LC_TOKENS + LC_PAD) * 2;
+  const size_t smem3 = ((size_t)2 * LC_TOKENS * (DIM + LC_PAD) + (size_t)VDIM * (LC_TOKENS + LC_PAD) + (size_t)2 * VDIM * (DIM + LC_PAD)) * 2;
+  SRB_CUDA_CALL(cudaFuncSetAttribute(lightning_chunk_states_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+  SRB_CUDA_CALL(cudaFuncSetAttribute(lightning_chunk_outputs_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
+  SRB_CUDA_CALL(srb_launch(lightning_activate_kernel, dim3(srb_sm_count() * 8), dim3(256), 0, s, const_cast<__nv_bfloat16*>(a.proj),
+                           a.pitch, rows, a.q_offset, a.heads * DIM, a.k_offset, a.heads * DIM, a.v_offset, a.heads * VDIM));
+  SRB_LAUNCH_CHECK("lightning_activate");
+  SRB_CUDA_CALL(srb_launch(lightning_chunk_states_kernel<DIM, VDIM>, dim3(chunks, a.heads), dim3(LC_THREADS), smem1, s, a));
+  SRB_LAUNCH_CHECK("lightning_chunk_states");
+  const int entries = DIM * VDIM;
+  SRB_CUDA_CALL(srb_launch(lightning_chunk_prefix_kernel, dim3((entries + 255) / 256, a.heads, a.requests), dim3(256), 0, s, a, entries));
+  SRB_LAUNCH_CHECK("lightning_chunk_prefix");
+  SRB_CUDA_CALL(srb_launch(lightning_chunk_outputs_kernel<DIM, VDIM>, dim3(chunks, a.heads), dim3(LC_THREADS), smem3, s, a));
+  SRB_LAUNCH_CHECK("lightning_chunk_outputs");
+  return SRB_OK;
+}
+
+// Tokens of a chunk, and whether these sizes are taken (bfloat16; dim and vdim 64 or 128 each).
+extern "C" int srb_lightning_chunk_tokens() { return LC_TOKENS; }
+extern "C" int srb_lightning_chunks_supports(int dim, int vdim, int dtype) {
+  return dtype == SRB_DTYPE_BF16 && (dim == 64 || dim == 128) && (vdim == 64 || vdim == 128);
+}
+
+// `chunks`: at least the number of chunks of the step, sum over the requests of ceil(rows / srb_lightning_chunk_tokens());
+// `chunk_states`: chunks * heads * dim * vdim floats of scratch.  The rest as for srb_lightning_scan, but: the q, k and v
+// columns of `proj` (`rows` rows) are replaced by their SiLU, and rows and column offsets lie on 16-byte borders.
+extern "C" int srb_lightning_chunks(void* proj, int rows, long long pitch, int q_offset, int k_offset, int v_offset,
+                                    const int* cu_rows, const int* positions, const int* state_slots, float* state,
+                                    const float* decay, float* chunk_states, float* out, int requests, int chunks, int heads,
+                                    int dim, int vdim, int read_only, void* stream) {
+  if (requests <= 0 || chunks <= 0) return SRB_OK;
+  if (!srb_lightning_chunks_supports(dim, vdim, SRB_DTYPE_BF16))
+    SRB_FAIL("lightning_chunks: a state of %d x %d per head is not taken (64 or 128 each)", dim, vdim);
+  if (heads <= 0 || heads > 65535 || requests > 65535) SRB_FAIL("lightning_chunks: %d heads or %d requests exceed one launch", heads, requests);
+  if (((pitch | q_offset | k_offset | v_offset) & 7) || ((uintptr_t)proj & 15))
+    SRB_FAIL("lightning_chunks: rows and the q, k, v columns must start on 16-byte borders");
+  if (rows <= 0) return SRB_OK;
+  LightningChunkArgs a;
+  a.proj = (const __nv_bfloat16*)proj; a.pitch = pitch; a.q_offset = q_offset; a.k_offset = k_offset; a.v_offset = v_offset;
+  a.cu_rows = cu_rows; a.positions = positions; a.state_slots = state_slots; a.state = state; a.decay = decay;
+  a.chunk_states = chunk_states; a.out = out; a.requests = requests; a.heads = heads; a.read_only = read_only;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dim == 64 && vdim == 64) return launch_lightning_chunks<64, 64>(a, rows, chunks, s);
+  if (dim == 64) return launch_lightning_chunks<64, 128>(a, rows, chunks, s);
+  if (vdim == 64) return launch_lightning_chunks<128, 64>(a, rows, chunks, s);
+  return launch_lightning_chunks<128, 128>(a, rows, chunks, s);
+}

@@ -123,9 +123,39 @@ struct StreamStepArgs {
   int streams, width, write_back, norm;
 };
 
-template <typename T>
+// four (VEC) or one consecutive columns of the result of the sublayer before, as floats
+template <typename T, int VEC>
+__device__ __forceinline__ void stream_load_result(const StreamStepArgs& a, const T* y, size_t row_offset, int i, float (&r)[VEC]) {
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) r[v] = 0.f;
+  if (y) {
+    if (VEC == 4 && sizeof(T) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(y + i);
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      r[0] = lo.x; r[1] = lo.y; r[VEC - 2] = hi.x; r[VEC - 1] = hi.y;
+    } else if (VEC == 4) {
+      const float4 raw = *reinterpret_cast<const float4*>(y + i);
+      r[0] = raw.x; r[1] = raw.y; r[VEC - 2] = raw.z; r[VEC - 1] = raw.w;
+    } else {
+      r[0] = srb_to_float(y[i]);
+    }
+  }
+  for (int part = 0; part < a.parts; ++part) {
+    const float* p = a.y_parts + part * a.part_stride + row_offset + i;
+    if (VEC == 4) {
+      const float4 raw = *reinterpret_cast<const float4*>(p);
+      r[0] += raw.x; r[1] += raw.y; r[VEC - 2] += raw.z; r[VEC - 1] += raw.w;
+    } else {
+      r[0] += *p;
+    }
+  }
+}
+
+// VEC 4: the row's width is a multiple of four and every pointer is 16-byte aligned; a thread moves four columns at a time.
+template <typename T, int VEC>
 __global__ void stream_step_kernel(StreamStepArgs a) {
-  extern __shared__ float staged[];                    // [width]: u of this row
+  extern __shared__ __align__(16) float staged[];      // [width]: u of this row
   __shared__ float reduce[33];
   __shared__ float coef[STREAMS_MAX * STREAMS_MAX + 2 * STREAMS_MAX];
   srb_launch_dependents();
@@ -142,40 +172,62 @@ __global__ void stream_step_kernel(StreamStepArgs a) {
   __syncthreads();
   const int src = a.row_index ? a.row_index[blockIdx.x] : blockIdx.x;
   float* x = a.x + (size_t)src * S * a.width;
-  const T* y = a.y ? reinterpret_cast<const T*>(a.y) + (size_t)src * a.width : nullptr;
+  const size_t row_offset = (size_t)src * a.width;
+  const T* y = a.y ? reinterpret_cast<const T*>(a.y) + row_offset : nullptr;
   float squares = 0.f;
-  for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
-    float old[STREAMS_MAX], fresh[STREAMS_MAX];
+  for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
+    float old[STREAMS_MAX][VEC], u[VEC];
 #pragma unroll
-    for (int s = 0; s < STREAMS_MAX; ++s)
-      if (s < S) old[s] = x[(size_t)s * a.width + i];
+    for (int s = 0; s < STREAMS_MAX; ++s) {
+      if (s < S) {
+        if (VEC == 4) {
+          const float4 raw = *reinterpret_cast<const float4*>(x + (size_t)s * a.width + i);
+          old[s][0] = raw.x; old[s][1] = raw.y; old[s][VEC - 2] = raw.z; old[s][VEC - 1] = raw.w;
+        } else {
+          old[s][0] = x[(size_t)s * a.width + i];
+        }
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) u[v] = 0.f;
     if (a.mix) {
-      float result = 0.f;
-      if (y) result = srb_to_float(y[i]);
-      for (int part = 0; part < a.parts; ++part) result += a.y_parts[part * a.part_stride + (size_t)src * a.width + i];
+      float result[VEC];
+      stream_load_result<T, VEC>(a, y, row_offset, i, result);
 #pragma unroll
       for (int t = 0; t < STREAMS_MAX; ++t) {
         if (t < S) {
-          float v = 0.f;
+          float fresh[VEC];
 #pragma unroll
-          for (int s = 0; s < STREAMS_MAX; ++s)
-            if (s < S) v = fmaf(mix[s * S + t], old[s], v);
-          fresh[t] = fmaf(spread[t], result, v);
-          if (a.write_back) x[(size_t)t * a.width + i] = fresh[t];
+          for (int v = 0; v < VEC; ++v) {
+            float sum = 0.f;
+#pragma unroll
+            for (int s = 0; s < STREAMS_MAX; ++s)
+              if (s < S) sum = fmaf(mix[s * S + t], old[s][v], sum);
+            fresh[v] = fmaf(spread[t], result[v], sum);
+            u[v] = fmaf(gather[t], fresh[v], u[v]);
+          }
+          if (a.write_back) {
+            if (VEC == 4)
+              *reinterpret_cast<float4*>(x + (size_t)t * a.width + i) = make_float4(fresh[0], fresh[1], fresh[VEC - 2], fresh[VEC - 1]);
+            else
+              x[(size_t)t * a.width + i] = fresh[0];
+          }
         }
       }
     } else {
 #pragma unroll
       for (int t = 0; t < STREAMS_MAX; ++t)
-        if (t < S) fresh[t] = old[t];
+        if (t < S) {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) u[v] = fmaf(gather[t], old[t][v], u[v]);
+        }
     }
     if (a.gather) {
-      float u = 0.f;
 #pragma unroll
-      for (int t = 0; t < STREAMS_MAX; ++t)
-        if (t < S) u = fmaf(gather[t], fresh[t], u);
-      staged[i] = u;
-      squares = fmaf(u, u, squares);
+      for (int v = 0; v < VEC; ++v) {
+        staged[i + v] = u[v];
+        squares = fmaf(u[v], u[v], squares);
+      }
     }
   }
   if (!a.gather) return;
@@ -187,10 +239,19 @@ __global__ void stream_step_kernel(StreamStepArgs a) {
     __syncthreads();
   }
   T* out = reinterpret_cast<T*>(a.out) + (size_t)blockIdx.x * a.out_pitch;
-  for (int i = threadIdx.x; i < a.width; i += blockDim.x) {
-    float v = staged[i] * inv;
-    if (a.weight) v *= a.weight[i];
-    out[i] = srb_from_float<T>(v);
+  for (int i = threadIdx.x * VEC; i < a.width; i += blockDim.x * VEC) {
+    float v[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = staged[i + k] * inv * (a.weight ? a.weight[i + k] : 1.f);
+    if (VEC == 4 && sizeof(T) == 2) {
+      uint2 raw;
+      *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[VEC - 2], v[VEC - 1]);
+      *reinterpret_cast<uint2*>(out + i) = raw;
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) out[i + k] = srb_from_float<T>(v[k]);
+    }
   }
 }
 
@@ -210,19 +271,24 @@ extern "C" int srb_stream_step(float* x, const void* y, const float* y_parts, in
   a.row_index = row_index; a.streams = streams; a.width = width; a.write_back = write_back && !row_index; a.norm = norm;
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) SRB_FAIL("stream_step: width %d exceeds what a block can stage", width);
-  const int threads = width >= 2048 ? 512 : 256;
+  const bool vec = width % 4 == 0 && part_stride % 4 == 0 && out_pitch % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)y | (uintptr_t)y_parts | (uintptr_t)out) & 15) == 0;
+  const int threads = vec ? (width >= 4096 ? 512 : 256) : (width >= 2048 ? 512 : 256);
   cudaStream_t s = (cudaStream_t)stream;
+#define STREAM_STEP_LAUNCH(T, VEC)                                                                                          \
+  do {                                                                                                                      \
+    if (smem > 48 * 1024)                                                                                                   \
+      SRB_CUDA_CALL(cudaFuncSetAttribute(stream_step_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    SRB_CUDA_CALL(srb_launch(stream_step_kernel<T, VEC>, dim3(rows), dim3(threads), smem, s, a));                           \
+  } while (0)
   if (dtype == SRB_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      SRB_CUDA_CALL(cudaFuncSetAttribute(stream_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SRB_CUDA_CALL(srb_launch(stream_step_kernel<float>, dim3(rows), dim3(threads), smem, s, a));
+    if (vec) STREAM_STEP_LAUNCH(float, 4); else STREAM_STEP_LAUNCH(float, 1);
   } else if (dtype == SRB_DTYPE_BF16) {
-    if (smem > 48 * 1024)
-      SRB_CUDA_CALL(cudaFuncSetAttribute(stream_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SRB_CUDA_CALL(srb_launch(stream_step_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, s, a));
+    if (vec) STREAM_STEP_LAUNCH(__nv_bfloat16, 4); else STREAM_STEP_LAUNCH(__nv_bfloat16, 1);
   } else {
     SRB_FAIL("stream_step: unknown dtype %d", dtype);
   }
+#undef STREAM_STEP_LAUNCH
   SRB_LAUNCH_CHECK("stream_step");
   return SRB_OK;
 }

@@ -1145,6 +1145,40 @@ def lightning_scan(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: i
         dtype_code(proj.dtype), _stream()))
 
 
+def lightning_chunks_takes(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """True if the tensor-core kernels for prompt portions take these sizes (the rule of srb_lightning_chunks_supports)."""
+    return dtype == torch.bfloat16 and dim in (64, 128) and vdim in (64, 128)
+
+
+#: tokens per chunk of :func:`lightning_chunks` (LC_TOKENS of csrc/lightning.cu)
+LIGHTNING_CHUNK_TOKENS = 64
+
+
+@traced("lightning")
+def lightning_chunks(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: int, cu_rows: torch.Tensor,
+                     positions: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
+                     out: torch.Tensor, requests: int, chunks: int, read_only: bool = False) -> None:
+    """What :func:`lightning_scan` computes, for prompt portions in bfloat16: the rows of every request are cut into
+    chunks of ``LIGHTNING_CHUNK_TOKENS`` tokens that run in parallel on the tensor cores (each chunk's own contribution
+    to the state, then the states before every chunk in order, then the results).  ``chunks``: the number of chunks of
+    the step, sum over the requests of ceil(rows / LIGHTNING_CHUNK_TOKENS), or more.  The q, k and v columns of ``proj``
+    are replaced by their SiLU on the way; rows and the three column offsets must lie on 16-byte borders."""
+    _need(proj, "proj", torch.bfloat16); _need(positions, "positions", torch.int32); _need(cu_rows, "cu_rows", torch.int32)
+    _need(state_slots, "state_slots", torch.int32); _need(state, "state", torch.float32); _need(decay, "decay", torch.float32)
+    _need(out, "out", torch.float32)
+    _, heads, dim, vdim = state.shape
+    if proj.dim() != 2 or decay.numel() != heads or out.shape != (proj.shape[0], heads * vdim):
+        raise KernelError("lightning_chunks: shapes of proj, the state, the decays and out do not agree")
+    if max(q_offset, k_offset) + heads * dim > proj.shape[1] or v_offset + heads * vdim > proj.shape[1]:
+        raise KernelError("lightning_chunks: rows of proj are too short")
+    scratch = torch.empty((max(int(chunks), 1), heads, dim, vdim), dtype=torch.float32, device=proj.device)
+    lib = load_library("lightning")
+    _check(lib, lib.srb_lightning_chunks(
+        _ptr(proj), proj.shape[0], ctypes.c_longlong(proj.stride(0)), q_offset, k_offset, v_offset, _ptr(cu_rows), _ptr(positions),
+        _ptr(state_slots), _ptr(state), _ptr(decay), _ptr(scratch), _ptr(out), int(requests), int(chunks), heads, dim, vdim,
+        int(read_only), _stream()), launches=4)
+
+
 @traced("lightning")
 def lightning_gate_norm(o: torch.Tensor, proj: torch.Tensor, g_offset: int, weight: torch.Tensor, eps: float,
                         out: torch.Tensor) -> None:

@@ -30,6 +30,9 @@ class LightningNames:
 
 class LightningAttention(Mixer):
     graph_safe = True
+    #: a step in which some request brings more rows than this runs the chunk-parallel kernels (bfloat16, states of 64
+    #: or 128 entries a side); steps of decoded tokens walk each request's rows in one block, from its state
+    CHUNKED_FROM = 8
 
     def __init__(self, hidden: int, heads: int, dim: int, vdim: int, decay: Sequence[float], eps: float,
                  names: LightningNames):
@@ -61,8 +64,16 @@ class LightningAttention(Mixer):
         qk, vv = self.heads * self.dim, self.heads * self.vdim
         proj = ops.linear(x, self.w_in, error_word=ctx.error_word)
         heads_out = torch.empty((rows, vv), dtype=torch.float32, device=x.device)
-        ops.lightning_scan(proj, 0, qk, 2 * qk, ctx.cu_rows, ctx.positions, ctx.state_slots, cache.state, self.decay,
-                           heads_out, ctx.num_requests, read_only=not cache.writable)
+        counts = [b - a for a, b in zip(ctx.host_cu_rows, ctx.host_cu_rows[1:])]
+        if (len(counts) == ctx.num_requests and max(counts, default=0) > self.CHUNKED_FROM
+                and ops.lightning_chunks_takes(proj.dtype, self.dim, self.vdim)):
+            # prompt portions: chunks in parallel on the tensor cores
+            chunks = sum(-(-count // ops.LIGHTNING_CHUNK_TOKENS) for count in counts)
+            ops.lightning_chunks(proj, 0, qk, 2 * qk, ctx.cu_rows, ctx.positions, ctx.state_slots, cache.state, self.decay,
+                                 heads_out, ctx.num_requests, chunks, read_only=not cache.writable)
+        else:
+            ops.lightning_scan(proj, 0, qk, 2 * qk, ctx.cu_rows, ctx.positions, ctx.state_slots, cache.state, self.decay,
+                               heads_out, ctx.num_requests, read_only=not cache.writable)
         gated = torch.empty((rows, vv), dtype=x.dtype, device=x.device)
         ops.lightning_gate_norm(heads_out, proj, 2 * qk + vv, self.norm, self.eps, gated)
         return ops.linear(gated, self.w_o, error_word=ctx.error_word, partial_ok=True)

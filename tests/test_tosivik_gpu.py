@@ -314,6 +314,56 @@ def test_linear_attention_over_states_in_slots(dtype, heads, dim, vdim):
         close(out2[part], want.reshape(-1, heads * vdim), torch.float32, f"second step, request {r}", 3e-5)
 
 
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 64, 128), (2, 128, 128), (2, 128, 64), (5, 64, 64)])
+def test_linear_attention_in_parallel_chunks_on_the_tensor_cores(heads, dim, vdim):
+    """Four requests in one step: a prompt of three chunks and a bit from position 0 in a slot that holds rubbish, a
+    portion that ends exactly at a chunk's end from a given state, a single token, and two tokens; then the next step
+    continues two of them.  q, k and v are the rounded activations; everything else is held to 32-bit accuracy."""
+    from sglang_rs_b200 import ops
+    torch.manual_seed(dim + vdim)
+    decay = [1.0, 0.3, 0.97, 0.999, 0.9][:heads]
+    counts, starts, slots = [201, 128, 1, 2], [0, 70, 9, 500], [2, 0, 3, 4]
+    total = sum(counts)
+    offsets = (8, 8 + heads * dim, 8 + 2 * heads * dim)
+    width = 8 + heads * (2 * dim + vdim) + 16
+    proj = torch.randn(total + 90, width)
+    state = torch.randn(6, heads, dim, vdim, device=DEV) * 0.5
+    given = state.cpu().double()
+
+    def parts(rows):
+        x = seen(proj[rows], torch.bfloat16)
+        def act(lo, n, d):
+            return seen(pt.silu(x[:, lo:lo + heads * d]), torch.bfloat16).view(-1, heads, d)
+        return act(offsets[0], heads, dim), act(offsets[1], heads, dim), act(offsets[2], heads, vdim)
+
+    def dev(values):
+        return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+    def run(rows, counts, starts, slots, begin_states, read_only=False):
+        cu = np.cumsum([0] + counts).tolist()
+        positions = [s + i for s, c in zip(starts, counts) for i in range(c)]
+        out = torch.full((sum(counts), heads * vdim), float("nan"), device=DEV)
+        chunks = sum(-(-c // ops.LIGHTNING_CHUNK_TOKENS) for c in counts)
+        ops.lightning_chunks(proj[rows].to(DEV, torch.bfloat16), *offsets, dev(cu), dev(positions), dev(slots), state,
+                             torch.tensor(decay, device=DEV), out, len(counts), chunks, read_only=read_only)
+        q, k, v = parts(rows)
+        after = []
+        for r in range(len(counts)):
+            part = slice(cu[r], cu[r + 1])
+            want, last = pt.linear_attention(q[part], k[part], v[part], decay, begin_states[r])
+            close(out[part], want.reshape(-1, heads * vdim), torch.float32, f"request {r}", 1e-4)
+            after.append(last)
+        return after
+    zero = torch.zeros(heads, dim, vdim, dtype=torch.float64)
+    after = run(slice(0, total), counts, starts, slots, [zero, given[0], given[3], given[4]])
+    for r in range(4):
+        close(state[slots[r]], after[r], torch.float32, f"state of request {r}", 1e-4)
+    close(state[1], given[1], torch.float32, "a slot that no request holds", 0.0)
+    before = state.clone()
+    run(slice(total, total + 90), [70, 20], [201, 198], [2, 0], [after[0], after[1]], read_only=True)
+    assert torch.equal(state, before)
+
+
 def test_linear_attention_with_a_decay_whose_powers_vanish():
     """600 tokens at a decay of 0.01: powers of the decay underflow to zero, and nothing becomes infinite or NaN."""
     from sglang_rs_b200 import ops
