@@ -49,6 +49,9 @@ SHAPES = {
     "qwen3-8b": {"num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
                  "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "tie_word_embeddings": False,
                  "context": 4096},
+    "qwen3-0.6b": {"num_hidden_layers": 28, "hidden_size": 1024, "num_attention_heads": 16, "num_key_value_heads": 8,
+                   "head_dim": 128, "intermediate_size": 3072, "vocab_size": 151936, "tie_word_embeddings": True,
+                   "context": 8192},
     "qwen3-1.7b": {"num_hidden_layers": 28, "hidden_size": 2048, "num_attention_heads": 16, "num_key_value_heads": 8,
                    "head_dim": 128, "intermediate_size": 6144, "vocab_size": 151936, "tie_word_embeddings": True,
                    "context": 8192},

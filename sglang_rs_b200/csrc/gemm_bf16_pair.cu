@@ -36,11 +36,12 @@ SRB_DEFINE_LAST_ERROR()
 #define PAIR_THREADS 192
 #define PAIR_EPI_BF16 0
 #define PAIR_EPI_SILU 2
+#define PAIR_EPI_ACT 5        // out = activation(x w^T): the plain kernel with an activation in its epilogue
 
 struct PairArgs {
   __nv_bfloat16* out;
   int tokens, features, k, ldo, up_row_offset;
-  int activation;            // which SRB_ACT_* the gated mode applies to the gate half
+  int activation;            // which SRB_ACT_* the gated mode applies to the gate half, or the plain mode to its result (-1: none)
   int tiles_t, tiles_f, num_tiles;
   int* error_word;
 };
@@ -237,7 +238,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             float acc[16];
             tmem_load_16(lane_address + b * PAIR_T + half * PAIR_OUT_T + c, acc);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) staged[(c + j) * FEATURES_PER_CTA + row_in_cta] = __float2bfloat16_rn(acc[j]);
+            for (int j = 0; j < 16; ++j)
+              staged[(c + j) * FEATURES_PER_CTA + row_in_cta] =
+                  __float2bfloat16_rn(args.activation >= 0 ? srb_gated<false>(args.activation, acc[j], 1.0f) : acc[j]);
           }
         }
         if (half == PAIR_T / PAIR_OUT_T - 1) {
@@ -309,7 +312,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 }
 
 // x [tokens, k] (row pitch ldx), w [rows_of_w, k] (row pitch ldw), out [tokens, ldo], all bfloat16; k and the
-// pitches multiples of 8.  mode 0: out = x w^T over `features` rows of w.  mode 2: w stacks gate rows
+// pitches multiples of 8.  mode 0: out = x w^T over `features` rows of w.  mode 5: out = activation(x w^T).  mode 2: w stacks gate rows
 // [0, features) and up rows [up_row_offset, up_row_offset + features); out = act(x gate^T) * (x up^T), act being SRB_ACT_* `activation` (activations.cuh).
 extern "C" int srb_gemm_bf16_pair(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
                                   int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int activation,
@@ -319,9 +322,10 @@ extern "C" int srb_gemm_bf16_pair(const void* x, const void* w, void* out, int t
     SRB_FAIL("gemm_bf16_pair: inner size %d and the row pitches %d, %d, %d must be positive multiples of 8", k, ldx, ldw,
              ldo);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) SRB_FAIL("gemm_bf16_pair: operands must be 16-byte aligned");
-  if (mode != PAIR_EPI_BF16 && mode != PAIR_EPI_SILU) SRB_FAIL("gemm_bf16_pair: unknown mode %d", mode);
-  if (mode == PAIR_EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT))
-    SRB_FAIL("gemm_bf16_pair: unknown activation %d", activation);
+  if (mode != PAIR_EPI_BF16 && mode != PAIR_EPI_SILU && mode != PAIR_EPI_ACT) SRB_FAIL("gemm_bf16_pair: unknown mode %d", mode);
+  if (mode == PAIR_EPI_BF16) activation = -1;
+  else if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("gemm_bf16_pair: unknown activation %d", activation);
+  if (mode == PAIR_EPI_ACT) mode = PAIR_EPI_BF16;            // the plain kernel; its epilogue applies `activation`
   if (mode == PAIR_EPI_SILU && up_row_offset + features > rows_of_w)
     SRB_FAIL("gemm_bf16_pair: the up rows lie outside the %d rows of w", rows_of_w);
   if (mode == PAIR_EPI_BF16 && features > rows_of_w) SRB_FAIL("gemm_bf16_pair: %d features exceed %d rows of w", features, rows_of_w);

@@ -156,6 +156,94 @@ extern "C" int srb_lightning_scan(const void* proj, long long pitch, int q_offse
   return SRB_OK;
 }
 
+// Steps of decoded tokens (every request brings one row): S <- decay S + k v^T and o = S^T q in one pass over the
+// state.  A block owns 32 value columns of one (request, head); its eight warps share the rows of the state (dim / 8
+// each, all of a thread's loads in flight together) and add their parts of o through shared memory in warp order.
+#define LD_COLUMNS 32
+#define LD_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(LD_COLUMNS * LD_WARPS) lightning_decode_kernel(LightningArgs a) {
+  extern __shared__ float ld_smem[];                 // q [dim], k [dim], partial results [LD_WARPS][LD_COLUMNS]
+  srb_launch_dependents();
+  const int head = blockIdx.x, request = blockIdx.y, c0 = blockIdx.z * LD_COLUMNS;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int dim = a.dim;
+  float* q = ld_smem;
+  float* k = q + dim;
+  float* part = k + dim;
+  const float decay = a.decay[head];
+  srb_grid_dependency_wait();
+  const int row = a.cu_rows[request];
+  if (a.cu_rows[request + 1] != row + 1) return;      // (the launcher is only used for steps of single rows)
+  const T* proj = reinterpret_cast<const T*>(a.proj) + (size_t)row * a.pitch;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    q[d] = la_silu(srb_to_float(proj[a.q_offset + head * dim + d]));
+    k[d] = la_silu(srb_to_float(proj[a.k_offset + head * dim + d]));
+  }
+  const int c = c0 + lane;
+  const bool live = c < a.vdim;
+  const float v = live ? la_silu(srb_to_float(proj[a.v_offset + head * a.vdim + c])) : 0.f;
+  const bool fresh = a.positions[row] == 0;           // a sequence's first token starts from the zero state
+  float* state = a.state + (((size_t)a.state_slots[request] * a.heads + head) * dim) * a.vdim + c;
+  __syncthreads();
+  const int per_warp = (dim + LD_WARPS - 1) / LD_WARPS;
+  const int d_begin = warp * per_warp, d_end = min(dim, d_begin + per_warp);
+  float acc = 0.f;
+  for (int d0 = d_begin; d0 < d_end; d0 += 8) {
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = (live && !fresh && d0 + i < d_end) ? state[(size_t)(d0 + i) * a.vdim] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (d0 + i < d_end) {
+        const float next = fmaf(decay, s[i], k[d0 + i] * v);
+        acc = fmaf(q[d0 + i], next, acc);
+        if (live && !a.read_only) state[(size_t)(d0 + i) * a.vdim] = next;
+      }
+    }
+  }
+  part[warp * LD_COLUMNS + lane] = acc;
+  __syncthreads();
+  if (warp == 0 && live) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < LD_WARPS; ++w) total += part[w * LD_COLUMNS + lane];
+    a.out[(size_t)row * a.heads * a.vdim + (size_t)head * a.vdim + c] = total;
+  }
+}
+
+// `single_rows` of srb_lightning_scan_step: every request of the step brings exactly one row.
+static int launch_lightning_decode(const LightningArgs& a, int requests, int dtype, cudaStream_t s) {
+  dim3 grid(a.heads, requests, (a.vdim + LD_COLUMNS - 1) / LD_COLUMNS);
+  if (grid.z > 65535 || a.heads > 65535) SRB_FAIL("lightning_scan: %d heads or %d value columns exceed one launch", a.heads, a.vdim);
+  const size_t smem = ((size_t)2 * a.dim + LD_WARPS * LD_COLUMNS) * sizeof(float);
+  if (smem > 48 * 1024) SRB_FAIL("lightning_scan: heads of %d entries do not fit", a.dim);
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(lightning_decode_kernel<float>, grid, dim3(LD_COLUMNS * LD_WARPS), smem, s, a));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(lightning_decode_kernel<__nv_bfloat16>, grid, dim3(LD_COLUMNS * LD_WARPS), smem, s, a));
+  else
+    SRB_FAIL("lightning_scan: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("lightning_decode");
+  return SRB_OK;
+}
+
+// srb_lightning_scan for a step in which every request brings exactly one row (decoded tokens; the caller knows it
+// from the step's shape, so nothing is decided from device memory).
+extern "C" int srb_lightning_scan_single(const void* proj, long long pitch, int q_offset, int k_offset, int v_offset,
+                                         const int* cu_rows, const int* positions, const int* state_slots, float* state,
+                                         const float* decay, float* out, int requests, int heads, int dim, int vdim,
+                                         int read_only, int dtype, void* stream) {
+  if (requests <= 0) return SRB_OK;
+  if (heads <= 0 || dim <= 0 || vdim <= 0) SRB_FAIL("lightning_scan: heads, dim and vdim must be positive");
+  if (requests > 65535) SRB_FAIL("lightning_scan: %d requests exceed one launch", requests);
+  LightningArgs a;
+  a.proj = proj; a.pitch = pitch; a.q_offset = q_offset; a.k_offset = k_offset; a.v_offset = v_offset;
+  a.cu_rows = cu_rows; a.positions = positions; a.state_slots = state_slots; a.state = state; a.decay = decay; a.out = out;
+  a.heads = heads; a.dim = dim; a.vdim = vdim; a.read_only = read_only; a.slices = 1; a.slice_width = vdim;
+  return launch_lightning_decode(a, requests, dtype, (cudaStream_t)stream);
+}
+
 // One block per row: the heads' results are normed together, scaled, gated and rounded.
 template <typename T>
 __global__ void lightning_gate_norm_kernel(const float* __restrict__ o, const T* __restrict__ proj, long long pitch,

@@ -956,11 +956,11 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mod
 def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
                    features: Optional[int] = None, up_row_offset: int = 0, activation: str = "silu") -> torch.Tensor:
     """y = x @ w^T for many tokens: 256 x 256 tiles on pairs of CTAs (``tcgen05.mma.cta_group::2``) in a
-    persistent kernel.  ``mode`` ``bf16`` or ``gated`` as in :func:`gemm_bf16`; the result is bfloat16."""
+    persistent kernel.  ``mode`` ``bf16``, ``gated`` or ``act`` as in :func:`gemm_bf16`; the result is bfloat16."""
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
     tokens, k = x.shape
     rows = w.shape[0]
-    if w.shape[1] != k or mode not in ("bf16", "gated"):
+    if w.shape[1] != k or mode not in ("bf16", "gated", "act"):
         raise KernelError(f"gemm_bf16_pair: x {tuple(x.shape)}, w {tuple(w.shape)} or mode {mode!r} do not fit")
     if features is None:
         features = rows
@@ -987,10 +987,13 @@ def gemm_bf16_takes(k: int) -> bool:
 def activated_product(x: torch.Tensor, weight: torch.Tensor, activation: str,
                       error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(x weight^T): the first product of a feed-forward without a gate.  bfloat16 with few rows: the tcgen05
-    kernel applies the activation in its epilogue; otherwise the product followed by the activation kernel."""
+    kernel applies the activation in its epilogue, and with many rows the CTA-pair kernel does; otherwise the product
+    followed by the activation kernel."""
     if (x.dtype == torch.bfloat16 and x.shape[0] <= OWN_GEMM_MAX_TOKENS and error_word is not None
             and gemm_bf16_takes(x.shape[1])):
         return gemm_bf16(x, weight, error_word, mode="act", activation=activation)
+    if (x.dtype == torch.bfloat16 and error_word is not None and pair_gemm_takes(x.shape[0], weight.shape[0], x.shape[1])):
+        return gemm_bf16_pair(x, weight, error_word, mode="act", activation=activation)
     up = linear(x, weight, error_word=error_word)
     activate(up, up, activation)
     return up
@@ -1121,8 +1124,10 @@ def stream_step(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.
 @traced("lightning")
 def lightning_scan(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: int, cu_rows: torch.Tensor,
                    positions: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
-                   out: torch.Tensor, requests: int, read_only: bool = False) -> None:
+                   out: torch.Tensor, requests: int, read_only: bool = False, single_rows: bool = False) -> None:
     """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v the SiLU of the row's projections.
+    ``single_rows``: every request of the step brings exactly one row (decoded tokens); a kernel that makes one pass
+    over the states then takes the step.
 
     ``proj`` [rows, *]: q heads (dim entries each) from column ``q_offset``, k heads from ``k_offset``, v heads
     (vdim each) from ``v_offset``; ``state`` float32 [slots, heads, dim, vdim], updated in place for the slots
@@ -1139,7 +1144,8 @@ def lightning_scan(proj: torch.Tensor, q_offset: int, k_offset: int, v_offset: i
     if max(q_offset, k_offset) + heads * dim > proj.shape[1] or v_offset + heads * vdim > proj.shape[1]:
         raise KernelError("lightning_scan: rows of proj are too short")
     lib = load_library("lightning")
-    _check(lib, lib.srb_lightning_scan(
+    entry = lib.srb_lightning_scan_single if single_rows else lib.srb_lightning_scan
+    _check(lib, entry(
         _ptr(proj), ctypes.c_longlong(proj.stride(0)), q_offset, k_offset, v_offset, _ptr(cu_rows), _ptr(positions),
         _ptr(state_slots), _ptr(state), _ptr(decay), _ptr(out), int(requests), heads, dim, vdim, int(read_only),
         dtype_code(proj.dtype), _stream()))

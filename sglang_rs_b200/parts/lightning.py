@@ -73,7 +73,8 @@ class LightningAttention(Mixer):
                                  heads_out, ctx.num_requests, chunks, read_only=not cache.writable)
         else:
             ops.lightning_scan(proj, 0, qk, 2 * qk, ctx.cu_rows, ctx.positions, ctx.state_slots, cache.state, self.decay,
-                               heads_out, ctx.num_requests, read_only=not cache.writable)
+                               heads_out, ctx.num_requests, read_only=not cache.writable,
+                               single_rows=len(counts) == ctx.num_requests and all(count == 1 for count in counts))
         gated = torch.empty((rows, vv), dtype=x.dtype, device=x.device)
         ops.lightning_gate_norm(heads_out, proj, 2 * qk + vv, self.norm, self.eps, gated)
         return ops.linear(gated, self.w_o, error_word=ctx.error_word, partial_ok=True)

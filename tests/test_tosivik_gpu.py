@@ -314,6 +314,39 @@ def test_linear_attention_over_states_in_slots(dtype, heads, dim, vdim):
         close(out2[part], want.reshape(-1, heads * vdim), torch.float32, f"second step, request {r}", 3e-5)
 
 
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 8, 12), (2, 128, 128), (1, 24, 70), (5, 6, 10), (4, 33, 32)])
+def test_linear_attention_of_a_step_of_decoded_tokens(dtype, heads, dim, vdim):
+    """Every request brings one row: one pass over the states.  One request is at position 0 in a slot that holds
+    rubbish; a read-only run leaves the states alone and gives the same results."""
+    from sglang_rs_b200 import ops
+    torch.manual_seed(dim * vdim)
+    decay = [1.0, 0.2, 0.97, 0.5, 0.999][:heads]
+    slots, positions = [3, 0, 5, 1], [17, 0, 400, 1]
+    width = heads * (2 * dim + vdim) + 5
+    proj = torch.randn(4, width)
+    state = torch.randn(6, heads, dim, vdim, device=DEV)
+    given = state.cpu().double()
+    offsets = (2, 2 + heads * dim, 2 + 2 * heads * dim)
+    x = seen(proj, dtype)
+    q = pt.silu(x[:, offsets[0]:offsets[0] + heads * dim]).view(4, heads, dim)
+    k = pt.silu(x[:, offsets[1]:offsets[1] + heads * dim]).view(4, heads, dim)
+    v = pt.silu(x[:, offsets[2]:offsets[2] + heads * vdim]).view(4, heads, vdim)
+
+    def dev(values):
+        return torch.tensor(values, dtype=torch.int32, device=DEV)
+    for read_only in (True, False):
+        out = torch.full((4, heads * vdim), float("nan"), device=DEV)
+        ops.lightning_scan(proj.to(DEV, dtype), *offsets, dev([0, 1, 2, 3, 4]), dev(positions), dev(slots), state,
+                           torch.tensor(decay, device=DEV), out, 4, read_only=read_only, single_rows=True)
+        for r in range(4):
+            begin = torch.zeros(heads, dim, vdim, dtype=torch.float64) if positions[r] == 0 else given[slots[r]]
+            want, after = pt.linear_attention(q[r:r + 1], k[r:r + 1], v[r:r + 1], decay, begin)
+            close(out[r:r + 1], want.reshape(1, -1), torch.float32, f"request {r}", 3e-5)
+            close(state[slots[r]], given[slots[r]] if read_only else after, torch.float32, f"state of request {r}", 3e-5)
+    close(state[2], given[2], torch.float32, "a slot that no request holds", 0.0)
+
+
 @pytest.mark.parametrize("heads,dim,vdim", [(3, 64, 128), (2, 128, 128), (2, 128, 64), (5, 64, 64)])
 def test_linear_attention_in_parallel_chunks_on_the_tensor_cores(heads, dim, vdim):
     """Four requests in one step: a prompt of three chunks and a bit from position 0 in a slot that holds rubbish, a
@@ -425,7 +458,7 @@ def test_experts_without_a_gate_with_a_router_bias_and_a_shared_expert(dtype, ex
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("rows", [3, 64, 200])
+@pytest.mark.parametrize("rows", [3, 64, 200, 1500])
 def test_feed_forward_without_a_gate_and_the_cap_on_logits(dtype, rows):
     from sglang_rs_b200 import ops
     from sglang_rs_b200.parts import PlainMlp
