@@ -51,7 +51,7 @@ def test_bench_command_runs_the_benchmark_of_the_repository(capsys):
 
 
 def test_trace_replay_options():
-    """``bin/trace_run``: the four options of its contract, and the three beside them."""
+    """``bin/trace_run``: the four options it must take, and the three beside them."""
     from sglang_rs_b200.engine.replay import DEFAULT_MAX_LIVE, PAGE_SIZE, build_parser as replay_parser
     args = replay_parser().parse_args(["--model", "/m", "--dtype", "float32", "--out", "/o", "--max-tokens", "640"])
     assert (args.model, args.dtype, args.out, args.max_tokens) == ("/m", "float32", "/o", 640)
