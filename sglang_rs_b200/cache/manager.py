@@ -312,7 +312,10 @@ class CacheManager:
             raise ValueError(f"request {request_id!r} is already live")
         handle = RequestCache(request_id, self, index)
         handle.length = self._lib.hc_length(self._pointer, index)
-        if self.has_state and self.device is not None:
+        # A request that found no free page is opened and closed again inside one scheduling call; by the time its
+        # events are read the books have no slot for it (a negative number), and no state may be touched: a negative
+        # index would name another request's slot.
+        if self.has_state and self.device is not None and handle.state_slot >= 0:
             for cache in self.layer_caches:
                 if isinstance(cache, StateLayerCache):
                     cache.state[handle.state_slot].zero_()       # a new request starts from zero state

@@ -181,3 +181,24 @@ def test_random_orders_lose_no_page(seed):
     cache.check_invariants()
     assert all(a.free_count == a.num_pages for a in cache.allocators.values())
     assert cache.state_pool.free_count == 4
+
+
+def test_a_request_that_was_opened_and_closed_before_its_handle_is_made_touches_no_state():
+    """The scheduler opens a request in the books, finds no free page for it and closes it again inside one call; the
+    manager reads both events afterwards.  The handle it makes for the request in between has no slot, and the states of
+    the live requests stay as they are."""
+    import torch
+    from sglang_rs_b200.cache import CacheManager
+    cache = CacheManager([RequestState((2,), torch.float32), PagedKV(2, 16)], page_size=16, max_tokens=64, max_requests=3,
+                         device="cpu", dtype=torch.float32)
+    live = [cache.open(name) for name in ("a", "b")]
+    state = cache.layer_cache(0).state
+    state[:] = 7.0
+    index = cache._lib.hc_open(cache._pointer)
+    assert index >= 0 and cache._lib.hc_close(cache._pointer, index) >= 0
+    ghost = cache.attach("ghost", index)
+    assert ghost.state_slot < 0
+    assert bool((state == 7.0).all())
+    cache.detach(ghost)
+    late = cache.open("c")                                   # a request that really starts does start from zero
+    assert float(state[late.state_slot].abs().sum()) == 0 and all(float(state[h.state_slot].min()) == 7.0 for h in live)

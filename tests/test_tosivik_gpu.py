@@ -615,6 +615,22 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype_name, stored)
     assert engine.cache.state_pool.free_count == engine.cache.max_requests
 
 
+def test_preemption_on_a_small_pool_gives_the_same_tokens(tmp_path):
+    """Three requests on a pool that cannot hold them: a request is preempted, gives its pages and its state slot back
+    and is computed again from its first token, in other portions and another slot; every token stays what the plain
+    implementation gives (32-bit)."""
+    from sglang_rs_b200 import Engine
+    folder = th.make_folder(tmp_path, "m", th.SMALL_A, seed=4, dtype=torch.float32)
+    doc, tensors = th.load_folder(folder)
+    prompts = list(th.random_requests(th.SMALL_A, (40, 35, 50), seed=2).values())
+    engine = Engine(model_path=folder, dtype="float32", page_size=16, max_total_tokens=160, max_running_requests=3,
+                    chunked_prefill_size=64)
+    results = engine.generate(prompts, {"max_new_tokens": 40})
+    assert engine.scheduler.stats["preemptions"] >= 1
+    assert [r["output_ids"] for r in results] == [th.plain_greedy(doc, tensors, p, 40) for p in prompts]
+    assert engine.cache.state_pool.free_count == engine.cache.max_requests
+
+
 def test_the_command_line_and_the_trace_program_take_the_design(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     config_path = tmp_path / "config.json"
