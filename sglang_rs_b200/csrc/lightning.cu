@@ -282,7 +282,7 @@ extern "C" int srb_lightning_gate_norm(const float* o, const void* proj, long lo
 }
 
 // ---- prompt portions in bfloat16: chunks in parallel, products on the tensor cores -------------------------------
-// The rows of every request are cut into chunks of LC_TOKENS tokens (from the request's first row of the step).  Three
+// The rows of every request are cut into chunks of LC_TOKENS (128) tokens (from the request's first row of the step).  Three
 // kernels behind one pass that replaces the q, k and v columns of the projection by their SiLU (rounded to bfloat16):
 //   1. per (chunk, head) the chunk's own contribution to the state, U = sum_j decay^(n-1-j) k_j v_j^T        (parallel)
 //   2. per (request, head, entry) the states before every chunk, S_(c+1) = decay^(n_c) S_c + U_c, walking the
@@ -295,8 +295,9 @@ extern "C" int srb_lightning_gate_norm(const float* o, const void* proj, long lo
 // bits of mantissa survive.  Operands lie in shared memory with the contraction index contiguous and rows padded by
 // 16 bytes, so a fragment is four (or two) conflict-free 32-bit loads.
 #include "mma_helpers.cuh"
-#define LC_TOKENS 64
+#define LC_TOKENS 128
 #define LC_THREADS 128
+#define LC_OUT_THREADS (LC_TOKENS * 2)      // the results kernel: a warp per sixteen rows of the chunk
 #define LC_PAD 8
 
 struct LightningChunkArgs {
@@ -380,29 +381,32 @@ __global__ void lightning_activate_kernel(__nv_bfloat16* proj, long long pitch, 
 // Loads a [LC_TOKENS, WIDTH] slice of the (activated) projection, transposed, into `dst` [WIDTH][TP]: consecutive lanes
 // take consecutive tokens, so the 2-byte stores of a warp fall into consecutive words.  `scale` (or null) gives a
 // factor per token; with it the product goes in as two bfloat16 numbers (dst, dst_lo).
-template <int WIDTH>
+template <int WIDTH, int THREADS>
 __device__ __forceinline__ void lc_load_transposed(const __nv_bfloat16* src, long long pitch, int n, const float* scale,
                                                    int scale_last, __nv_bfloat16* dst, __nv_bfloat16* dst_lo) {
-  constexpr int TP = LC_TOKENS + LC_PAD, ITEMS = LC_TOKENS * WIDTH / 8, PER = ITEMS / LC_THREADS;
-  Bf16x8 x[PER];
+  constexpr int TP = LC_TOKENS + LC_PAD, ITEMS = LC_TOKENS * WIDTH / 8, PER = ITEMS / THREADS, BATCH = PER < 8 ? PER : 8;
+#pragma unroll 1
+  for (int first = 0; first < PER; first += BATCH) {          // eight loads of a thread in flight at a time
+    Bf16x8 x[BATCH];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int item = threadIdx.x + i * LC_THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
-    x[i] = lc_load8(src + (size_t)j * pitch + d0, j < n);
-  }
+    for (int i = 0; i < BATCH; ++i) {
+      const int item = threadIdx.x + (first + i) * THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
+      x[i] = lc_load8(src + (size_t)j * pitch + d0, j < n);
+    }
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int item = threadIdx.x + i * LC_THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
-    const float factor = (scale && j < n) ? scale[scale_last - j] : 0.f;
+    for (int i = 0; i < BATCH; ++i) {
+      const int item = threadIdx.x + (first + i) * THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
+      const float factor = (scale && j < n) ? scale[scale_last - j] : 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      if (scale) {
-        __nv_bfloat16 hi, lo;
-        lc_split(factor * __bfloat162float(x[i].v[k]), hi, lo);
-        dst[(d0 + k) * TP + j] = hi;
-        dst_lo[(d0 + k) * TP + j] = lo;
-      } else {
-        dst[(d0 + k) * TP + j] = x[i].v[k];
+      for (int k = 0; k < 8; ++k) {
+        if (scale) {
+          __nv_bfloat16 hi, lo;
+          lc_split(factor * __bfloat162float(x[i].v[k]), hi, lo);
+          dst[(d0 + k) * TP + j] = hi;
+          dst_lo[(d0 + k) * TP + j] = lo;
+        } else {
+          dst[(d0 + k) * TP + j] = x[i].v[k];
+        }
       }
     }
   }
@@ -423,8 +427,8 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_states_kernel(Ligh
   int request, row0, n;
   if (!lc_find(a, blockIdx.x, request, row0, n)) return;
   __syncthreads();
-  lc_load_transposed<DIM>(a.proj + (size_t)row0 * a.pitch + a.k_offset + head * DIM, a.pitch, n, power, n - 1, kt_hi, kt_lo);
-  lc_load_transposed<VDIM>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  lc_load_transposed<DIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.k_offset + head * DIM, a.pitch, n, power, n - 1, kt_hi, kt_lo);
+  lc_load_transposed<VDIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   constexpr int MT = DIM / 64;                 // m16 tiles per warp: the warp owns DIM / 4 rows of U
@@ -508,7 +512,7 @@ __global__ void lightning_chunk_prefix_kernel(LightningChunkArgs a, int entries)
 }
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(LC_THREADS) lightning_chunk_outputs_kernel(LightningChunkArgs a) {
+__global__ void __launch_bounds__(LC_OUT_THREADS) lightning_chunk_outputs_kernel(LightningChunkArgs a) {
   constexpr int DP = DIM + LC_PAD, TP = LC_TOKENS + LC_PAD;
   extern __shared__ __align__(16) unsigned char lc_smem[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(lc_smem);          // [LC_TOKENS][DP]
@@ -525,38 +529,39 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_outputs_kernel(Lig
   if (!lc_find(a, blockIdx.x, request, row0, n)) return;
   {
     // q and k as they lie: 16-byte pieces, a row's pieces in consecutive lanes
-    constexpr int PIECES = LC_TOKENS * DIM / 8, PER = PIECES / LC_THREADS;
+    constexpr int PIECES = LC_TOKENS * DIM / 8, PER = PIECES / LC_OUT_THREADS;
     Bf16x8 xq[PER], xk[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int piece = threadIdx.x + i * LC_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
+      const int piece = threadIdx.x + i * LC_OUT_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
       const __nv_bfloat16* row = a.proj + (size_t)(row0 + j) * a.pitch + head * DIM + d0;
       xq[i] = lc_load8(row + a.q_offset, j < n);
       xk[i] = lc_load8(row + a.k_offset, j < n);
     }
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int piece = threadIdx.x + i * LC_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
+      const int piece = threadIdx.x + i * LC_OUT_THREADS, j = piece / (DIM / 8), d0 = piece % (DIM / 8) * 8;
       *reinterpret_cast<uint4*>(qs + j * DP + d0) = *reinterpret_cast<const uint4*>(xq[i].v);
       *reinterpret_cast<uint4*>(ks + j * DP + d0) = *reinterpret_cast<const uint4*>(xk[i].v);
     }
   }
-  lc_load_transposed<VDIM>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  lc_load_transposed<VDIM, LC_OUT_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
   {
     // the state before the chunk, [d][c] floats, into [c][d] as two bfloat16 numbers: consecutive lanes take
     // consecutive d, four columns each
     const float* before = a.chunk_states + ((size_t)blockIdx.x * a.heads + head) * DIM * VDIM;
     constexpr int ITEMS = DIM * VDIM / 4, BATCH = 8;
-    for (int first = 0; first < ITEMS; first += BATCH * LC_THREADS) {
+    for (int first = 0; first < ITEMS; first += BATCH * LC_OUT_THREADS) {
       float4 x[BATCH];
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int item = first + threadIdx.x + i * LC_THREADS, d = item % DIM, c0 = item / DIM * 4;
-        x[i] = *reinterpret_cast<const float4*>(before + (size_t)d * VDIM + c0);
+        const int item = first + threadIdx.x + i * LC_OUT_THREADS, d = item % DIM, c0 = item / DIM * 4;
+        x[i] = item < ITEMS ? *reinterpret_cast<const float4*>(before + (size_t)d * VDIM + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int item = first + threadIdx.x + i * LC_THREADS, d = item % DIM, c0 = item / DIM * 4;
+        const int item = first + threadIdx.x + i * LC_OUT_THREADS, d = item % DIM, c0 = item / DIM * 4;
+        if (item >= ITEMS) continue;
         const float v[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -657,7 +662,7 @@ static int launch_lightning_chunks(const LightningChunkArgs& a, int rows, int ch
   const int entries = DIM * VDIM;
   SRB_CUDA_CALL(srb_launch(lightning_chunk_prefix_kernel, dim3((entries + 255) / 256, a.heads, a.requests), dim3(256), 0, s, a, entries));
   SRB_LAUNCH_CHECK("lightning_chunk_prefix");
-  SRB_CUDA_CALL(srb_launch(lightning_chunk_outputs_kernel<DIM, VDIM>, dim3(chunks, a.heads), dim3(LC_THREADS), smem3, s, a));
+  SRB_CUDA_CALL(srb_launch(lightning_chunk_outputs_kernel<DIM, VDIM>, dim3(chunks, a.heads), dim3(LC_OUT_THREADS), smem3, s, a));
   SRB_LAUNCH_CHECK("lightning_chunk_outputs");
   return SRB_OK;
 }

@@ -1157,7 +1157,7 @@ def lightning_chunks_takes(dtype: torch.dtype, dim: int, vdim: int) -> bool:
 
 
 #: tokens per chunk of :func:`lightning_chunks` (LC_TOKENS of csrc/lightning.cu)
-LIGHTNING_CHUNK_TOKENS = 64
+LIGHTNING_CHUNK_TOKENS = 128
 
 
 @traced("lightning")
