@@ -355,7 +355,7 @@ def test_linear_attention_in_parallel_chunks_on_the_tensor_cores(heads, dim, vdi
     from sglang_rs_b200 import ops
     torch.manual_seed(dim + vdim)
     decay = [1.0, 0.3, 0.97, 0.999, 0.9][:heads]
-    counts, starts, slots = [201, 128, 1, 2], [0, 70, 9, 500], [2, 0, 3, 4]
+    counts, starts, slots = [401, 256, 1, 2], [0, 70, 9, 500], [2, 0, 3, 4]
     total = sum(counts)
     offsets = (8, 8 + heads * dim, 8 + 2 * heads * dim)
     width = 8 + heads * (2 * dim + vdim) + 16
@@ -393,7 +393,7 @@ def test_linear_attention_in_parallel_chunks_on_the_tensor_cores(heads, dim, vdi
         close(state[slots[r]], after[r], torch.float32, f"state of request {r}", 1e-4)
     close(state[1], given[1], torch.float32, "a slot that no request holds", 0.0)
     before = state.clone()
-    run(slice(total, total + 90), [70, 20], [201, 198], [2, 0], [after[0], after[1]], read_only=True)
+    run(slice(total, total + 90), [70, 20], [401, 326], [2, 0], [after[0], after[1]], read_only=True)
     assert torch.equal(state, before)
 
 
